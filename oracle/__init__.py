@@ -1,0 +1,187 @@
+"""numpy front end of the CPU oracle (``w8a8_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the
+CPU-baseline legs of ``bench.py``.  The shipped package never imports it.
+
+bf16 and f16 tensors travel as ``uint16`` arrays of raw bits; int8 codes as ``int8``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside it; returns the library path."""
+    src = os.path.join(_HERE, "w8a8_oracle.c")
+    stale = (not os.path.exists(_SO)) or os.path.getmtime(_SO) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = ctypes.CDLL(_SO)
+        _lib.oracle_exp.restype = ctypes.c_float
+        _lib.oracle_exp.argtypes = [ctypes.c_float]
+        _lib.oracle_threads.restype = ctypes.c_int
+    return _lib
+
+
+def _p(a: np.ndarray):
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _sz(v: int):
+    return ctypes.c_size_t(int(v))
+
+
+def threads() -> int:
+    return int(lib().oracle_threads())
+
+
+# ------------------------------------------------------------------ conversions
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().oracle_f32_to_f16(_p(x), _p(out), _sz(x.size))
+    return out
+
+
+def f16_bits_to_f32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().oracle_f16_to_f32(_p(x), _p(out), _sz(x.size))
+    return out
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().oracle_f32_to_bf16(_p(x), _p(out), _sz(x.size))
+    return out
+
+
+def bf16_bits_to_f32(x: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(x, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def exp(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return np.array([lib().oracle_exp(float(v)) for v in x.ravel()], dtype=np.float32).reshape(x.shape)
+
+
+# ------------------------------------------------------------------ prologues
+def _q_out(tokens: int, out_stride: int, fill: int) -> np.ndarray:
+    return np.full((tokens, out_stride), fill, dtype=np.uint8).view(np.int8)
+
+
+def prepare_norm_i8(h, norm_scale, mod_scale, mod_shift, width, out_stride, eps=1e-5, fill=0):
+    """h: uint16 bf16 bits [tokens][width] -> (q int8 [tokens][out_stride], q_scale f32 [tokens])."""
+    h = np.ascontiguousarray(h, dtype=np.uint16).reshape(-1, width)
+    tokens = h.shape[0]
+    ns, ms, sh = (np.ascontiguousarray(v, dtype=np.float32) for v in (norm_scale, mod_scale, mod_shift))
+    q, s = _q_out(tokens, out_stride, fill), np.zeros(tokens, dtype=np.float32)
+    lib().oracle_prepare_norm_i8(_sz(tokens), _p(h), _p(ns), _p(ms), _p(sh), _p(q), _p(s), _sz(width),
+                                 _sz(out_stride), ctypes.c_float(eps))
+    return q, s
+
+
+def prepare_gated_i8(attn, gate, width, out_stride, gate_stride, fill=0):
+    """attn: f16 bits [tokens][width]; gate: f16 bits [tokens][gate_stride]."""
+    attn = np.ascontiguousarray(attn, dtype=np.uint16).reshape(-1, width)
+    gate = np.ascontiguousarray(gate, dtype=np.uint16).reshape(-1, gate_stride)
+    tokens = attn.shape[0]
+    q, s = _q_out(tokens, out_stride, fill), np.zeros(tokens, dtype=np.float32)
+    lib().oracle_prepare_gated_i8(_sz(tokens), _p(attn), _p(gate), _p(q), _p(s), _sz(width), _sz(out_stride),
+                                  _sz(gate_stride))
+    return q, s
+
+
+def prepare_plain_i8(h, width, out_stride, fill=0):
+    """h: f16 bits [tokens][width]."""
+    h = np.ascontiguousarray(h, dtype=np.uint16).reshape(-1, width)
+    tokens = h.shape[0]
+    q, s = _q_out(tokens, out_stride, fill), np.zeros(tokens, dtype=np.float32)
+    lib().oracle_prepare_plain_i8(_sz(tokens), _p(h), _p(q), _p(s), _sz(width), _sz(out_stride))
+    return q, s
+
+
+# ------------------------------------------------------------------ GEMMs
+def gemm_i8_acc(a, w, k_size, k_stride, n_size):
+    """a: int8 [m][k_stride], w: int8 [n][k_stride] -> i32 [m][n]."""
+    a = np.ascontiguousarray(a, dtype=np.int8).reshape(-1, k_stride)
+    w = np.ascontiguousarray(w, dtype=np.int8).reshape(n_size, k_stride)
+    m = a.shape[0]
+    acc = np.empty((m, n_size), dtype=np.int32)
+    lib().oracle_gemm_i8_acc(_sz(m), _p(a), _p(w), _p(acc), _sz(k_size), _sz(k_stride), _sz(n_size))
+    return acc
+
+
+def epilogue_plain(acc, scale, a_scale):
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    m, n = acc.shape
+    scale, a_scale = np.ascontiguousarray(scale, np.float32), np.ascontiguousarray(a_scale, np.float32)
+    c = np.empty((m, n), dtype=np.uint16)
+    lib().oracle_epilogue_plain(_sz(m), _p(acc), _p(scale), _p(a_scale), _p(c), _sz(n))
+    return c
+
+
+def epilogue_resid(acc, scale, a_scale, c, gate):
+    """Returns the updated bf16 residual (the input array is not modified)."""
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    m, n = acc.shape
+    scale, a_scale, gate = (np.ascontiguousarray(v, np.float32) for v in (scale, a_scale, gate))
+    out = np.array(c, dtype=np.uint16, copy=True).reshape(m, n)
+    lib().oracle_epilogue_resid(_sz(m), _p(acc), _p(scale), _p(a_scale), _p(out), _p(gate), _sz(n))
+    return out
+
+
+def epilogue_swiglu(acc, scale, a_scale):
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    m, n = acc.shape
+    scale, a_scale = np.ascontiguousarray(scale, np.float32), np.ascontiguousarray(a_scale, np.float32)
+    c = np.empty((m, n // 2), dtype=np.uint16)
+    lib().oracle_epilogue_swiglu(_sz(m), _p(acc), _p(scale), _p(a_scale), _p(c), _sz(n))
+    return c
+
+
+def gemm_i8_256(a, w, scale, a_scale, k_size, k_stride, n_size):
+    return epilogue_plain(gemm_i8_acc(a, w, k_size, k_stride, n_size), scale, a_scale)
+
+
+def gemm_i8_resid_256(a, w, scale, a_scale, c, gate, k_size, k_stride, n_size):
+    return epilogue_resid(gemm_i8_acc(a, w, k_size, k_stride, n_size), scale, a_scale, c, gate)
+
+
+def gemm_i8_swiglu_256(a, w, scale, a_scale, k_size, k_stride, n_size):
+    return epilogue_swiglu(gemm_i8_acc(a, w, k_size, k_stride, n_size), scale, a_scale)
+
+
+def transport_bf16_to_f16(x):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty_like(x)
+    lib().oracle_transport_bf16_to_f16(_p(x), _p(out), _sz(x.size))
+    return out
+
+
+def transport_f16_to_bf16(x):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty_like(x)
+    lib().oracle_transport_f16_to_bf16(_p(x), _p(out), _sz(x.size))
+    return out
