@@ -1,0 +1,217 @@
+/*
+ * krea2_b200 -- C ABI of the B200 (sm_100a) implementation of krea2-hrx's W8A8
+ * linear-layer path.
+ *
+ * The reference has no C ABI of its own: its boundary is the kernel launch ABI that
+ * `Session::launch` (src/session/mod.rs:386-421) and `Ops::launch` (src/ops/mod.rs:673-693)
+ * hand to the runtime -- an exported symbol `krea2_<stem>`, one packed scalar (the row
+ * count) and the buffers in the order of each kernel's `launch(...)` signature, with the
+ * shape constants supplied as compile-time `config` keys.  Each function below keeps one
+ * such symbol: same name, same buffer order, and the config keys as trailing integers.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless a parameter is named host_*; `stream` is a
+ *    `cudaStream_t` (passed as void* so that this header needs no CUDA include).
+ *  - The caller owns every buffer; kernels allocate nothing.  Bytes of a row beyond
+ *    `width` / `k_size` are never read (GEMM operands) and never written (prologues).
+ *  - bf16 and f16 tensors are raw 16-bit patterns, row-major.
+ *  - Every function returns a krea2_status; on failure krea2_last_error() returns a
+ *    thread-local description.  Invalid arguments are refused before any device work
+ *    (the reference's rule, tests/constructor.rs).
+ */
+#ifndef KREA2_B200_H
+#define KREA2_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error classes of krea2::Error (src/error.rs:10-29). */
+typedef enum krea2_status {
+    KREA2_OK = 0,
+    KREA2_INVALID_ARGUMENT = 1,
+    KREA2_CANCELLED = 2,
+    KREA2_POISONED = 3,
+    KREA2_RUNTIME = 4, /* a CUDA call failed, or a kernel reported a bounded wait that ran out */
+    KREA2_INTERNAL = 5
+} krea2_status;
+
+typedef void *krea2_stream; /* cudaStream_t */
+
+/* Thread-local message of the last failing call on this thread ("" when none). */
+const char *krea2_last_error(void);
+/* Library version string. */
+const char *krea2_version(void);
+/* Reads and clears the device-side status word the GEMM sets when one of its bounded
+ * waits gives up (0 = healthy).  Synchronises the device. */
+int krea2_device_status(int *host_status);
+
+/* ---------------------------------------------------------------- activation prologues */
+
+/* kernels/prepare_norm_i8.loom:11-22.  h bf16 [tokens][width]; norm_scale, mod_scale,
+ * mod_shift f32 [width]; q int8 [tokens][out_stride]; q_scale f32 [tokens].
+ * width in 2048..32768 step 2048; out_stride multiple of 64, >= width. */
+int krea2_prepare_norm_i8(krea2_stream stream, size_t tokens, const void *h, const float *norm_scale,
+                          const float *mod_scale, const float *mod_shift, void *q, float *q_scale,
+                          size_t width, size_t out_stride, float eps);
+
+/* kernels/prepare_gated_i8.loom:11-22.  attn f16 [tokens][width]; gate f16 rows of pitch
+ * gate_stride (multiple of 256, >= width) whose first `width` columns are used. */
+int krea2_prepare_gated_i8(krea2_stream stream, size_t tokens, const void *attn, const void *gate, void *q,
+                           float *q_scale, size_t width, size_t out_stride, size_t gate_stride);
+
+/* kernels/prepare_plain_i8.loom:10-19.  h f16 [tokens][width]. */
+int krea2_prepare_plain_i8(krea2_stream stream, size_t tokens, const void *h, void *q, float *q_scale,
+                           size_t width, size_t out_stride);
+
+/* ---------------------------------------------------------------- int8 GEMMs
+ * a int8 [m][k_stride], w int8 [n_size][k_stride] (both K-contiguous), scale f32 [n_size]
+ * (per output channel), a_scale f32 [m] (per token).  k_size multiple of 128 (64 for the
+ * 256x256 export), n_size multiple of 128 (256), k_stride multiple of 64 and >= k_size,
+ * m in 1..2^24.  m_group (1..4) and schedule_rows (0/1) are the reference's scheduling
+ * hints: range-checked, without numerical effect. */
+
+/* kernels/gemm_i8_256.loom:14-36.  c f16 [m][n_size] = f16(bf16((acc*scale[n])*a_scale[m])). */
+int krea2_gemm_i8_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                      const float *a_scale, void *c, size_t k_size, size_t k_stride, size_t n_size,
+                      size_t m_group);
+
+/* kernels/gemm_i8_resid_256.loom:14-36.  c bf16 [m][n_size] in/out:
+ * c = bf16(c + bf16(gate[n] * bf16((acc*scale[n])*a_scale[m]))); gate f32 [n_size]. */
+int krea2_gemm_i8_resid_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                            const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride,
+                            size_t n_size, size_t m_group);
+
+/* kernels/gemm_i8_resid_256x256.loom:16-42.  Same arithmetic on the wide tile's constraints. */
+int krea2_gemm_i8_resid_256x256(krea2_stream stream, size_t m, const void *a, const void *w,
+                                const float *scale, const float *a_scale, void *c, const float *gate,
+                                size_t k_size, size_t k_stride, size_t n_size, size_t m_group,
+                                size_t schedule_rows);
+
+/* kernels/gemm_i8_swiglu_256.loom:16-38.  w rows interleaved [gate o..o+15 | up o..o+15];
+ * c f16 [m][n_size/2] = f16(bf16(bf16(silu(g)) * u)). */
+int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                             const float *a_scale, void *c, size_t k_size, size_t k_stride, size_t n_size,
+                             size_t m_group);
+
+/* The raw i32 accumulators acc [m][n_size] of the same contraction, for parity checks
+ * (the reference's tests recompute them on the CPU, tests/quantized.rs:203-211). */
+int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
+                      size_t k_size, size_t k_stride, size_t n_size);
+
+/* bf16 <-> f16 transport of src/training/quantized.rs:63-72,102-110 (`lora_transport`,
+ * reverse = 1: bf16 -> f16, reverse = 2: f16 -> bf16). */
+int krea2_lora_transport(krea2_stream stream, size_t elements, const void *src, void *dst, int reverse);
+
+/* ---------------------------------------------------------------- generic dispatch
+ * Ops::launch (src/ops/mod.rs:673-693): kernel by stem, config keys by name, packed
+ * scalars, buffers in binding order, and the launch geometry the reference would use
+ * (checked against the kernel's rules, then ignored: the B200 kernels size their own grid). */
+typedef struct krea2_config_entry {
+    const char *key; /* e.g. "k_size"; "eps" takes its value from the float field */
+    uint64_t value;
+    float fvalue;
+} krea2_config_entry;
+
+typedef struct krea2_binding {
+    void *ptr;    /* device pointer */
+    size_t bytes; /* extent the kernel may touch from ptr */
+} krea2_binding;
+
+int krea2_launch(krea2_stream stream, const char *name, const krea2_config_entry *config, size_t config_count,
+                 const uint64_t *indices, size_t index_count, const krea2_binding *bindings,
+                 size_t binding_count, size_t grid_x, size_t grid_y, uint32_t threads);
+
+/* ---------------------------------------------------------------- launch-shape rules
+ * src/kernels/shape.rs:8-112. */
+size_t krea2_shape_tokens_min(void);
+size_t krea2_shape_tokens_max(void);
+size_t krea2_shape_capacity(size_t tokens);
+size_t krea2_shape_gemm_pitch(size_t k);
+size_t krea2_shape_gemm_grid_rows(size_t tokens);
+size_t krea2_shape_gemm_m_group(void);
+int krea2_shape_gemm_schedule_rows(size_t tokens);
+size_t krea2_shape_attention_rows(size_t tokens);
+/* tile of a bundle stem ("gemm_qkvg", "gemm_gu", "gemm_wo", "gemm_down"): columns and threads. */
+size_t krea2_shape_gemm_tile_columns(const char *stem);
+uint32_t krea2_shape_gemm_tile_threads(const char *stem);
+/* kernel source name of a family on that stem's tile (shape::gemm_source). */
+const char *krea2_shape_gemm_source(const char *family, const char *stem);
+
+/* ---------------------------------------------------------------- resident session
+ * krea2::session::Session (src/session/mod.rs:147-588) over synthetic or caller-supplied
+ * weights laid out by the checkpoint plan's rules (src/checkpoint/plan.rs:88-226,
+ * src/session/weights.rs:47-125). */
+typedef struct krea2_dims {
+    size_t hidden;   /* residual width d            (reference: 6144)  */
+    size_t kv_heads; /* key/value heads             (reference: 12)    */
+    size_t head_dim; /* channels per head           (reference: 128)   */
+    size_t inter;    /* SwiGLU inner width          (reference: 16384) */
+} krea2_dims;
+
+typedef struct krea2_weights krea2_weights;
+typedef struct krea2_session krea2_session;
+
+/* Session::validate_dimensions (src/session/mod.rs:278-287): no device is touched. */
+int krea2_session_validate_dimensions(size_t tokens, size_t layers);
+
+/* Bytes of the one device allocation that holds `layers` blocks at kernel pitches, each
+ * span starting on a 256-byte boundary in name order (plan.rs:135-141). */
+int krea2_weights_plan_bytes(const krea2_dims *dims, size_t layers, size_t *bytes);
+/* Allocates that block on the current device.  krea2_weights_locate gives the device
+ * address and byte length of a span by the plan's names ("blocks.3.qkvg.q", "blocks.3.gu.s",
+ * "blocks.0.prenorm", ...; session/weights.rs:112-125). */
+int krea2_weights_create(const krea2_dims *dims, size_t layers, krea2_weights **out);
+int krea2_weights_locate(const krea2_weights *weights, const char *name, void **ptr, size_t *bytes);
+/* Fills every span with seeded synthetic values on the device: int8 rows uniform in
+ * [-127, 127], channel scales uniform in [1e-3, 1e-2], norm scales ~N(0, 0.1). */
+int krea2_weights_fill_synthetic(krea2_weights *weights, uint64_t seed, krea2_stream stream);
+/* Host-side upload of one span (rows are re-pitched by the caller's layout = plan layout). */
+int krea2_weights_upload(krea2_weights *weights, const char *name, const void *host_bytes, size_t bytes,
+                         krea2_stream stream);
+void krea2_weights_retain(krea2_weights *weights);
+void krea2_weights_release(krea2_weights *weights);
+
+/* Session::with_weights (src/session/mod.rs:265-276): buffers at shape::capacity(tokens)
+ * rows, zero-filled headroom, bound to `stream` (calls on another stream are refused,
+ * :375-380). */
+int krea2_session_create(krea2_stream stream, krea2_weights *weights, size_t tokens, size_t layers,
+                         krea2_session **out);
+void krea2_session_destroy(krea2_session *session);
+size_t krea2_session_tokens(const krea2_session *session);
+size_t krea2_session_layers(const krea2_session *session);
+/* Session::set_profile (:367-373): returns the previous setting. */
+int krea2_session_set_profile(krea2_session *session, int enable);
+/* After a profiled forward: per-stage device milliseconds, stage labels as the reference's
+ * (:461-494).  Returns the number of stages written (<= capacity). */
+size_t krea2_session_stage_profile(const krea2_session *session, const char **labels, double *millis,
+                                   size_t capacity);
+
+/* Session::run (:502-540): HOST x bf16 [tokens][hidden] in/out, HOST mods f32
+ * [layers][6][hidden], HOST cos/sin f32 [tokens][head_dim]; uploads, runs blocks
+ * first_block..first_block+block_count eagerly, reads x back (blocking).
+ * block_count 0 means "to the last layer". */
+int krea2_session_run(krea2_session *session, krea2_stream stream, uint16_t *host_x, const float *host_mods,
+                      const float *host_cos, const float *host_sin, size_t first_block, size_t block_count);
+
+/* Session::run_device (:553-588): DEVICE x and mods; copies them into the session's fixed
+ * buffers, replays the recorded graph of all layers, copies x back; asynchronous on `stream`.
+ * x_bytes / mods_bytes are the extents of the caller's views. */
+int krea2_session_run_device(krea2_session *session, krea2_stream stream, void *x, size_t x_bytes,
+                             const void *mods, size_t mods_bytes, const float *host_cos,
+                             const float *host_sin);
+
+/* Device address of a session buffer by name ("x", "a_q", "a_s", "fused", "attn_gu",
+ * "mods"), for tests that compare intermediates. */
+int krea2_session_buffer(const krea2_session *session, const char *name, void **ptr, size_t *bytes);
+
+/* Number of kernels of this library that one forward of `layers` blocks launches. */
+size_t krea2_session_launches_per_forward(const krea2_session *session);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KREA2_B200_H */

@@ -1,0 +1,84 @@
+// Shared host/device helpers of the krea2_b200 library: the error channel of the C ABI
+// and the f32 arithmetic whose every step is one IEEE operation (no contraction, no
+// fast-math), so that results do not depend on compiler flags.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/krea2_b200.h"
+
+namespace krea2 {
+
+// ---------------------------------------------------------------- error channel
+// Records the message of a failing call for krea2_last_error() and returns `status`.
+int fail(krea2_status status, const char *format, ...);
+void clear_error();
+
+#define KREA2_CUDA(call)                                                                        \
+    do {                                                                                        \
+        cudaError_t status_ = (call);                                                           \
+        if (status_ != cudaSuccess)                                                             \
+            return ::krea2::fail(KREA2_RUNTIME, "%s failed: %s", #call, cudaGetErrorString(status_)); \
+    } while (0)
+
+#define KREA2_REQUIRE(condition, ...)                                                           \
+    do {                                                                                        \
+        if (!(condition)) return ::krea2::fail(KREA2_INVALID_ARGUMENT, __VA_ARGS__);            \
+    } while (0)
+
+// Defined with the GEMM: first-use initialisation done ahead of a stream capture.
+int prepare_gemm_device();
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------- device arithmetic
+#ifdef __CUDACC__
+
+// f32 -> bf16 -> f32, round to nearest even (the `fptrunc ... to bf16` + `extf` pairs of the
+// reference kernels; src/numerics.rs:18-26 states the rule).
+__device__ __forceinline__ float bf_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// f32 -> f16 -> f32, IEEE round to nearest even.
+__device__ __forceinline__ float hf_round(float x) { return __half2float(__float2half_rn(x)); }
+
+// exp with a fixed evaluation order: Cody-Waite reduction by ln 2 in two pieces, the degree-6
+// Cephes polynomial, scaling by two exact powers of two.  It stands in for the reference's
+// approximate `expf<afn>` (kernels/prepare_gated_i8.loom:99, gemm_i8_swiglu_256.loom:650).
+__device__ __forceinline__ float canonical_exp(float x) {
+    if (x != x) return x;
+    if (x > 88.72283935546875f) return __int_as_float(0x7f800000);
+    if (x < -104.0f) return 0.0f;
+    float t = __fmul_rn(x, 1.44269502162933349609375f);
+    float n = rintf(t);
+    float r = __fmaf_rn(n, -0.693359375f, x);
+    r = __fmaf_rn(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    float r2 = __fmul_rn(r, r);
+    float y = __fmaf_rn(p, r2, r);
+    y = __fadd_rn(y, 1.0f);
+    int ni = (int)n;
+    int h1 = ni / 2, h2 = ni - h1;
+    float a = __int_as_float((h1 + 127) << 23);
+    float b = __int_as_float((h2 + 127) << 23);
+    return __fmul_rn(__fmul_rn(y, a), b);
+}
+
+// 1 / (1 + exp(0 - g)), unrounded f32 (kernels/prepare_gated_i8.loom:98-101).
+__device__ __forceinline__ float sigmoid_f32(float g) {
+    float e = canonical_exp(__fsub_rn(0.0f, g));
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace krea2

@@ -1,0 +1,605 @@
+// The W8A8 GEMM family of krea2-hrx for sm_100a:
+//   krea2_gemm_i8_256, krea2_gemm_i8_resid_256, krea2_gemm_i8_resid_256x256,
+//   krea2_gemm_i8_swiglu_256  (kernels/gemm_i8_*.loom), plus the raw-accumulator variant.
+//
+// One persistent, warp-specialised kernel, templated on the epilogue and the N tile:
+//   warp 4      TMA producer: int8 A [128 x 128B] and W [BN x 128B] tiles, 128-byte swizzle,
+//               into a ring of shared-memory stages, completion on mbarriers
+//   warp 5      one thread issues tcgen05.mma kind::i8 (128 x BN x 32 per instruction),
+//               accumulating i32 in tensor memory; tcgen05.commit frees the stage
+//   warps 0-3   epilogue: tcgen05.ld of the 128 x BN accumulator (one row per thread),
+//               i32 -> f32, weight-channel and token scales, the bf16 rounding points of
+//               the reference and the residual / SwiGLU / plain store
+// Two accumulators alternate in tensor memory, so the epilogue of one tile runs under the
+// main loop of the next.  No cluster is launched and no load is multicast.
+//
+// Every wait on an mbarrier is bounded in time; a wait that runs out raises a CTA-wide
+// abort flag and a device status word, the roles fall through to the common teardown, the
+// producer drains its loads in flight, tensor memory is released and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace krea2 {
+
+__device__ int g_device_status = 0;
+
+namespace {
+
+constexpr int kBlockM = 128;        // accumulator rows = TMEM lanes
+constexpr int kBlockK = 128;        // bytes of K per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 32;          // K of one kind::i8 instruction
+constexpr int kEpilogueWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after two seconds
+
+enum class Epi { Plain, Resid, Swiglu, Acc };
+
+enum StatusBits { kProducerTimedOut = 1, kMmaTimedOut = 2, kEpilogueTimedOut = 4, kDrainTimedOut = 8 };
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Waits for the phase of `parity` to complete.  Returns false when the CTA is aborting or
+// when the wait ran out of time (in which case it raises the abort flag and `bit`).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int bit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(&g_device_status, bit);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i).
+__device__ __forceinline__ void tmem_load_32(uint32_t address, int32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte
+// swizzled, eight rows (1024 bytes) per swizzle atom: start address, leading offset 1
+// (unused by this layout), stride 1024 between atoms, descriptor version 1, swizzle mode 2.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+    return static_cast<uint64_t>((address & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::i8: i32 accumulate (2 at bit 4), signed 8-bit A and B
+// (1 at bits 7 and 10), both K-major, N/8 at bit 17, M/16 at bit 24.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- kernel
+template <int BN>
+struct Tile {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = kBlockM * kBlockK;
+    static constexpr int kBBytes = BN * kBlockK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemColumns = 2 * BN;
+    // stages, then barriers (full, empty per stage; full, empty per accumulator), the TMEM
+    // base and the abort flag; 1024 spare bytes to align the stages.
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+struct GemmArgs {
+    uint32_t m, n, k_blocks;
+    const float *scale;    // [n] per output channel
+    const float *a_scale;  // [m] per token
+    const float *gate;     // [n], residual epilogue only
+    void *c;               // f16 [m][n] | bf16 [m][n] in/out | f16 [m][n/2] | i32 [m][n]
+};
+
+__device__ __forceinline__ float dequant(int32_t acc, float ws, float as) {
+    // kernels/gemm_i8_256.loom:610-620: sitofp, times the channel scale, times the token scale, bf16.
+    return bf_round(__fmul_rn(__fmul_rn(__int2float_rn(acc), ws), as));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
+    __nv_bfloat162 b = __halves2bfloat162(__float2bfloat16_rn(lo), __float2bfloat16_rn(hi));
+    return *reinterpret_cast<uint32_t *>(&b);
+}
+
+// One thread's 32 consecutive accumulator columns of one row, starting at column n.
+template <Epi E>
+__device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const GemmArgs &g, uint32_t row, uint32_t n,
+                                               float as) {
+    float ws[32];
+    if constexpr (E != Epi::Acc) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            *reinterpret_cast<float4 *>(ws + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.scale + n) + i);
+    }
+    if constexpr (E == Epi::Plain) {
+        uint4 *out = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                w[i] = pack_half2(dequant(acc[8 * v + 2 * i], ws[8 * v + 2 * i], as),
+                                  dequant(acc[8 * v + 2 * i + 1], ws[8 * v + 2 * i + 1], as));
+            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else if constexpr (E == Epi::Resid) {
+        // kernels/gemm_i8_resid_256.loom:622-635: bf16(lin), bf16(lin * gate), bf16(prior + gated).
+        uint4 *x = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
+        float gt[32];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            *reinterpret_cast<float4 *>(gt + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.gate + n) + i);
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            uint4 prior = x[v];
+            const uint32_t pw[4] = {prior.x, prior.y, prior.z, prior.w};
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int c = 8 * v + 2 * i;
+                float lo = bf_round(__fmul_rn(dequant(acc[c], ws[c], as), gt[c]));
+                float hi = bf_round(__fmul_rn(dequant(acc[c + 1], ws[c + 1], as), gt[c + 1]));
+                lo = __fadd_rn(__uint_as_float(pw[i] << 16), lo);
+                hi = __fadd_rn(__uint_as_float(pw[i] & 0xffff0000u), hi);
+                w[i] = pack_bf162(lo, hi);
+            }
+            x[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else if constexpr (E == Epi::Swiglu) {
+        // kernels/gemm_i8_swiglu_256.loom:612-660: columns n..n+15 are gate rows, n+16..n+31 the
+        // matching up rows; 16 outputs at column n/2.
+        uint4 *out =
+            reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * (g.n / 2) + n / 2);
+#pragma unroll
+        for (int v = 0; v < 2; v++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float r[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int o = 8 * v + 2 * i + h;
+                    float gv = dequant(acc[o], ws[o], as);
+                    float uv = dequant(acc[o + 16], ws[o + 16], as);
+                    float silu = bf_round(__fmul_rn(gv, sigmoid_f32(gv)));
+                    r[h] = bf_round(__fmul_rn(silu, uv));
+                }
+                w[i] = pack_half2(r[0], r[1]);
+            }
+            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        uint4 *out = reinterpret_cast<uint4 *>(static_cast<int32_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
+#pragma unroll
+        for (int v = 0; v < 8; v++) out[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+    }
+}
+
+template <Epi E, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const GemmArgs g) {
+    using T = Tile<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + T::kStages * T::kStageBytes);
+    uint64_t *empty = full + T::kStages;
+    uint64_t *acc_full = empty + T::kStages;
+    uint64_t *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
+    const uint32_t tiles = m_tiles * (g.n / BN);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::kStages; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(acc_full + a, 1);
+            mbar_init(acc_empty + a, kEpilogueWarps * 32);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tmem_alloc(tmem_slot, T::kTmemColumns);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kProducerWarp) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x) {
+                const int m0 = static_cast<int>(tile % m_tiles) * kBlockM;
+                const int n0 = static_cast<int>(tile / m_tiles) * BN;
+                for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
+                    if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, kProducerTimedOut)) {
+                        alive = false;
+                        break;
+                    }
+                    uint8_t *a_dst = smem + stage * T::kStageBytes;
+                    mbar_expect_tx(full + stage, T::kStageBytes);
+                    tma_load_2d(a_dst, &map_a, full + stage, static_cast<int>(kb) * kBlockK, m0);
+                    tma_load_2d(a_dst + T::kABytes, &map_w, full + stage, static_cast<int>(kb) * kBlockK, n0);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == T::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (*abort_flag) {
+                // Drain: no load of this CTA may still be writing shared memory when it exits.
+                const uint64_t start = global_timer_ns();
+                for (int s = 0; s < T::kStages; s++) {
+                    if (!(armed & (1u << s))) continue;
+                    while (!mbar_try_wait(full + s, (armed_parity >> s) & 1u)) {
+                        if (global_timer_ns() - start > kWaitLimitNs) {
+                            atomicOr(&g_device_status, kDrainTimedOut);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instruction_descriptor(kBlockM, BN);
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool alive = true;
+            for (uint32_t tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x, local++) {
+                const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
+                if (!mbar_wait(acc_empty + a, a_phase ^ 1u, abort_flag, kMmaTimedOut)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + a * BN;
+                for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
+                    if (!mbar_wait(full + stage, phase, abort_flag, kMmaTimedOut)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * T::kStageBytes);
+                    const uint64_t a_desc = smem_descriptor(a_addr);
+                    const uint64_t b_desc = smem_descriptor(a_addr + T::kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; k++) {
+                        // 32 bytes further along K inside the swizzled row: +2 in 16-byte units.
+                        umma_i8(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty + stage);
+                    if (++stage == T::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (alive) umma_commit(acc_full + a);
+            }
+        }
+    } else {
+        // Epilogue warps 0..3: warp w reads TMEM lanes 32w..32w+31, one accumulator row per thread.
+        uint32_t local = 0;
+        for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, local++) {
+            const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
+            const uint32_t m0 = (tile % m_tiles) * kBlockM, n0 = (tile / m_tiles) * BN;
+            const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            tc_fence_after();
+            const uint32_t row = m0 + warp * 32 + lane;
+            const bool in_range = row < g.m;
+            float as = 0.0f;
+            if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
+            const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                int32_t acc[32];
+                tmem_load_32(lane_base + c * 32, acc);
+                if (in_range) epilogue_chunk<E>(acc, g, row, n0 + c * 32, as);
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty + a);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, T::kTmemColumns);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+// int8 [rows][k_stride] viewed as a 2-D tensor (k_size x rows), boxes of 128 bytes x box_rows,
+// 128-byte swizzle; out-of-range rows and K read as zero.
+int make_operand_map(CUtensorMap *map, const void *base, size_t rows, size_t k_size, size_t k_stride,
+                     uint32_t box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {k_size, rows};
+    cuuint64_t strides[1] = {k_stride};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box,
+                        element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+    return KREA2_OK;
+}
+
+int sm_count() {
+    static int cached[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (cached[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
+// Raises the kernel's dynamic shared-memory limit once per device.
+template <Epi E, int BN>
+int ensure_instance() {
+    static std::once_flag once[64];
+    static cudaError_t attr_status[64];
+    int device = 0;
+    KREA2_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
+    std::call_once(once[device], [&] {
+        attr_status[device] = cudaFuncSetAttribute(gemm_i8_kernel<E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   Tile<BN>::kSmemBytes);
+    });
+    if (attr_status[device] != cudaSuccess)
+        return fail(KREA2_RUNTIME, "cannot reserve %d bytes of shared memory: %s", Tile<BN>::kSmemBytes,
+                    cudaGetErrorString(attr_status[device]));
+    return KREA2_OK;
+}
+
+template <Epi E, int BN>
+int launch_instance(cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_w, const GemmArgs &args) {
+    if (int status = ensure_instance<E, BN>()) return status;
+    const uint32_t tiles = ((args.m + kBlockM - 1) / kBlockM) * (args.n / BN);
+    const unsigned grid = tiles < static_cast<uint32_t>(sm_count()) ? tiles : static_cast<unsigned>(sm_count());
+    gemm_i8_kernel<E, BN><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_w, args);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 launch failed: %s", cudaGetErrorString(status));
+    return KREA2_OK;
+}
+
+// The `config.decl` ranges of the GEMM kernels (kernels/gemm_i8_256.loom:14-22,
+// gemm_i8_resid_256x256.loom:16-27) and the row-count bound (:97).
+int check_gemm(const char *name, size_t m, size_t k_size, size_t k_stride, size_t n_size, size_t m_group,
+               size_t k_multiple, size_t n_multiple) {
+    KREA2_REQUIRE(m >= 1 && m <= 16777216, "%s: m %zu outside 1..16777216", name, m);
+    KREA2_REQUIRE(k_size >= k_multiple && k_size <= 65536 && k_size % k_multiple == 0,
+                  "%s: k_size %zu must be a multiple of %zu up to 65536", name, k_size, k_multiple);
+    KREA2_REQUIRE(n_size >= n_multiple && n_size <= 32768 && n_size % n_multiple == 0,
+                  "%s: n_size %zu must be a multiple of %zu up to 32768", name, n_size, n_multiple);
+    KREA2_REQUIRE(k_stride >= 64 && k_stride <= 65536 && k_stride % 64 == 0 && k_stride >= k_size,
+                  "%s: k_stride %zu must be a multiple of 64 up to 65536 and at least k_size", name, k_stride);
+    KREA2_REQUIRE(m_group >= 1 && m_group <= 4, "%s: m_group %zu outside 1..4", name, m_group);
+    return KREA2_OK;
+}
+
+template <Epi E>
+int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, const void *w, const float *scale,
+             const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride, size_t n_size) {
+    KREA2_REQUIRE(a && w && c, "%s: null buffer", name);
+    KREA2_REQUIRE(aligned16(a) && aligned16(w) && aligned16(c), "%s: buffers must be 16-byte aligned", name);
+    if constexpr (E != Epi::Acc) {
+        KREA2_REQUIRE(scale && a_scale && aligned16(scale), "%s: scale vectors missing or not 16-byte aligned", name);
+    }
+    if constexpr (E == Epi::Resid) {
+        KREA2_REQUIRE(gate && aligned16(gate), "%s: gate vector missing or not 16-byte aligned", name);
+    }
+    GemmArgs args;
+    args.m = static_cast<uint32_t>(m);
+    args.n = static_cast<uint32_t>(n_size);
+    args.k_blocks = static_cast<uint32_t>((k_size + kBlockK - 1) / kBlockK);
+    args.scale = scale;
+    args.a_scale = a_scale;
+    args.gate = gate;
+    args.c = c;
+    const bool wide = n_size % 256 == 0;
+    CUtensorMap map_a, map_w;
+    if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
+    if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, wide ? 256 : 128)) return status;
+    return wide ? launch_instance<E, 256>(stream, map_a, map_w, args)
+                : launch_instance<E, 128>(stream, map_a, map_w, args);
+}
+
+}  // namespace
+
+// Everything a later launch would otherwise do on first use (driver entry point, shared
+// memory limits), so that a launch inside a stream capture issues nothing but the kernel.
+int prepare_gemm_device() {
+    if (!encode_tiled()) return fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled is not available from this driver");
+    sm_count();
+    if (int s = ensure_instance<Epi::Plain, 128>()) return s;
+    if (int s = ensure_instance<Epi::Plain, 256>()) return s;
+    if (int s = ensure_instance<Epi::Resid, 128>()) return s;
+    if (int s = ensure_instance<Epi::Resid, 256>()) return s;
+    if (int s = ensure_instance<Epi::Swiglu, 128>()) return s;
+    if (int s = ensure_instance<Epi::Swiglu, 256>()) return s;
+    if (int s = ensure_instance<Epi::Acc, 128>()) return s;
+    if (int s = ensure_instance<Epi::Acc, 256>()) return s;
+    return KREA2_OK;
+}
+
+}  // namespace krea2
+
+using namespace krea2;
+
+extern "C" int krea2_gemm_i8_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                                 const float *a_scale, void *c, size_t k_size, size_t k_stride, size_t n_size,
+                                 size_t m_group) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_256", m, k_size, k_stride, n_size, m_group, 128, 128)) return status;
+    return run_gemm<Epi::Plain>("gemm_i8_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale, c, nullptr,
+                                k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_resid_256(krea2_stream stream, size_t m, const void *a, const void *w,
+                                       const float *scale, const float *a_scale, void *c, const float *gate,
+                                       size_t k_size, size_t k_stride, size_t n_size, size_t m_group) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_resid_256", m, k_size, k_stride, n_size, m_group, 128, 128)) return status;
+    return run_gemm<Epi::Resid>("gemm_i8_resid_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale, c,
+                                gate, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_resid_256x256(krea2_stream stream, size_t m, const void *a, const void *w,
+                                           const float *scale, const float *a_scale, void *c, const float *gate,
+                                           size_t k_size, size_t k_stride, size_t n_size, size_t m_group,
+                                           size_t schedule_rows) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_resid_256x256", m, k_size, k_stride, n_size, m_group, 64, 256))
+        return status;
+    KREA2_REQUIRE(schedule_rows <= 1, "gemm_i8_resid_256x256: schedule_rows %zu outside 0..1", schedule_rows);
+    return run_gemm<Epi::Resid>("gemm_i8_resid_256x256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale,
+                                c, gate, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const void *a, const void *w,
+                                        const float *scale, const float *a_scale, void *c, size_t k_size,
+                                        size_t k_stride, size_t n_size, size_t m_group) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_swiglu_256", m, k_size, k_stride, n_size, m_group, 128, 128)) return status;
+    return run_gemm<Epi::Swiglu>("gemm_i8_swiglu_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale, c,
+                                 nullptr, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
+                                 size_t k_size, size_t k_stride, size_t n_size) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_acc", m, k_size, k_stride, n_size, 1, 64, 128)) return status;
+    return run_gemm<Epi::Acc>("gemm_i8_acc", static_cast<cudaStream_t>(stream), m, a, w, nullptr, nullptr, acc,
+                              nullptr, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_device_status(int *host_status) {
+    clear_error();
+    KREA2_REQUIRE(host_status, "device_status: null output");
+    KREA2_CUDA(cudaDeviceSynchronize());
+    int value = 0;
+    KREA2_CUDA(cudaMemcpyFromSymbol(&value, g_device_status, sizeof(int)));
+    if (value != 0) {
+        int zero = 0;
+        KREA2_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    }
+    *host_status = value;
+    return KREA2_OK;
+}
