@@ -172,6 +172,9 @@ int krea2_weights_fill_synthetic(krea2_weights *weights, uint64_t seed, krea2_st
 /* Host-side upload of one span (rows are re-pitched by the caller's layout = plan layout). */
 int krea2_weights_upload(krea2_weights *weights, const char *name, const void *host_bytes, size_t bytes,
                          krea2_stream stream);
+/* Blocking read of one span back into host memory (the same layout upload takes). */
+int krea2_weights_download(const krea2_weights *weights, const char *name, void *host_bytes, size_t bytes,
+                           krea2_stream stream);
 void krea2_weights_retain(krea2_weights *weights);
 void krea2_weights_release(krea2_weights *weights);
 

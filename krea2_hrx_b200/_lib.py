@@ -92,6 +92,7 @@ SIGNATURES = {
     "krea2_weights_locate": (c_int, [c_void_p, c_char_p, POINTER(c_void_p), POINTER(c_size_t)]),
     "krea2_weights_fill_synthetic": (c_int, [c_void_p, c_uint64, c_void_p]),
     "krea2_weights_upload": (c_int, [c_void_p, c_char_p, c_void_p, c_size_t, c_void_p]),
+    "krea2_weights_download": (c_int, [c_void_p, c_char_p, c_void_p, c_size_t, c_void_p]),
     "krea2_weights_retain": (None, [c_void_p]),
     "krea2_weights_release": (None, [c_void_p]),
     "krea2_session_create": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, POINTER(c_void_p)]),

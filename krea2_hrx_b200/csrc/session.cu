@@ -211,7 +211,7 @@ const char *const kStageLabels[kStagesPerBlock] = {
 
 // One block's launches in the reference's order (src/session/mod.rs:671-840).  `events`, when
 // given, receives kStagesPerBlock + 1 recorded events bracketing the stages.
-int run_block(krea2_session *s, size_t index, cudaEvent_t *events) {
+int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *events) {
     BlockPointers w{};
     if (int status = block_pointers(s, index, &w)) return status;
     const krea2_dims &d = s->dims;
@@ -221,7 +221,7 @@ int run_block(krea2_session *s, size_t index, cudaEvent_t *events) {
     const float *mods = s->mods + index * 6 * hidden;  // prescale, preshift, pregate, postscale, postshift, postgate
     int stage = 0;
     auto mark = [&]() -> int {
-        if (events) KREA2_CUDA(cudaEventRecord(events[stage], s->stream));
+        if (events) KREA2_CUDA(cudaEventRecord(events[stage], stream));
         stage++;
         return KREA2_OK;
     };
@@ -229,23 +229,23 @@ int run_block(krea2_session *s, size_t index, cudaEvent_t *events) {
 #define KREA2_STEP(call)                    \
     if ((status = mark())) return status;   \
     if ((status = (call))) return status;
-    KREA2_STEP(krea2_prepare_norm_i8(s->stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph, 1e-5f))
-    KREA2_STEP(krea2_gemm_i8_256(s->stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
+    KREA2_STEP(krea2_prepare_norm_i8(stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph, 1e-5f))
+    KREA2_STEP(krea2_gemm_i8_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
     {
         if ((status = mark())) return status;
         KREA2_CUDA(cudaMemcpy2DAsync(s->attn_gu, hidden * 2, s->fused, s->qkvg * 2, hidden * 2, t,
-                                     cudaMemcpyDeviceToDevice, s->stream));
+                                     cudaMemcpyDeviceToDevice, stream));
     }
-    KREA2_STEP(krea2_prepare_gated_i8(s->stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q, s->a_s, hidden, ph,
+    KREA2_STEP(krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q, s->a_s, hidden, ph,
                                       s->qkvg))
-    KREA2_STEP(krea2_gemm_i8_resid_256(s->stream, t, s->a_q, w.wo_q, w.wo_s, s->a_s, s->x, mods + 2 * hidden, hidden, ph,
+    KREA2_STEP(krea2_gemm_i8_resid_256(stream, t, s->a_q, w.wo_q, w.wo_s, s->a_s, s->x, mods + 2 * hidden, hidden, ph,
                                        hidden, group))
-    KREA2_STEP(krea2_prepare_norm_i8(s->stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q, s->a_s,
+    KREA2_STEP(krea2_prepare_norm_i8(stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q, s->a_s,
                                      hidden, ph, 1e-5f))
-    KREA2_STEP(krea2_gemm_i8_swiglu_256(s->stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu, hidden, ph, 2 * inter,
+    KREA2_STEP(krea2_gemm_i8_swiglu_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu, hidden, ph, 2 * inter,
                                         group))
-    KREA2_STEP(krea2_prepare_plain_i8(s->stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
-    KREA2_STEP(krea2_gemm_i8_resid_256x256(s->stream, t, s->a_q, w.down_q, w.down_s, s->a_s, s->x, mods + 5 * hidden,
+    KREA2_STEP(krea2_prepare_plain_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
+    KREA2_STEP(krea2_gemm_i8_resid_256x256(stream, t, s->a_q, w.down_q, w.down_s, s->a_s, s->x, mods + 5 * hidden,
                                            inter, pi, hidden, group,
                                            static_cast<size_t>(krea2_shape_gemm_schedule_rows(t))))
 #undef KREA2_STEP
@@ -266,11 +266,20 @@ int upload_rope(krea2_session *s, const float *host_cos, const float *host_sin) 
 }
 
 int record_graph(krea2_session *s) {
+    // Captured on a stream of its own: the session's stream may be the legacy default stream,
+    // which cannot be captured.  Capturing executes nothing; the graph is launched on s->stream.
     cudaGraph_t graph = nullptr;
-    KREA2_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    cudaStream_t capture = nullptr;
+    KREA2_CUDA(cudaStreamCreateWithFlags(&capture, cudaStreamNonBlocking));
+    cudaError_t begin = cudaStreamBeginCapture(capture, cudaStreamCaptureModeThreadLocal);
+    if (begin != cudaSuccess) {
+        cudaStreamDestroy(capture);
+        return fail(KREA2_RUNTIME, "cannot begin a stream capture: %s", cudaGetErrorString(begin));
+    }
     int status = KREA2_OK;
-    for (size_t i = 0; i < s->layers && status == KREA2_OK; i++) status = run_block(s, i, nullptr);
-    cudaError_t end = cudaStreamEndCapture(s->stream, &graph);
+    for (size_t i = 0; i < s->layers && status == KREA2_OK; i++) status = run_block(s, capture, i, nullptr);
+    cudaError_t end = cudaStreamEndCapture(capture, &graph);
+    cudaStreamDestroy(capture);
     if (status != KREA2_OK) {
         if (graph) cudaGraphDestroy(graph);
         return status;
@@ -292,7 +301,7 @@ int run_profiled(krea2_session *s, size_t first, size_t count) {
         for (size_t i = old; i < s->events.size(); i++) KREA2_CUDA(cudaEventCreate(&s->events[i]));
     }
     for (size_t i = 0; i < count; i++)
-        if (int status = run_block(s, first + i, s->events.data() + i * per)) return status;
+        if (int status = run_block(s, s->stream, first + i, s->events.data() + i * per)) return status;
     KREA2_CUDA(cudaStreamSynchronize(s->stream));
     s->stages.clear();
     for (size_t i = 0; i < count; i++)
@@ -393,6 +402,19 @@ extern "C" int krea2_weights_upload(krea2_weights *weights, const char *name, co
     KREA2_REQUIRE(bytes == it->second.bytes, "%s spans %zu bytes, got %zu", name, it->second.bytes, bytes);
     KREA2_CUDA(cudaMemcpyAsync(weights->base + it->second.offset, host_bytes, bytes, cudaMemcpyHostToDevice,
                                static_cast<cudaStream_t>(stream)));
+    return KREA2_OK;
+}
+
+extern "C" int krea2_weights_download(const krea2_weights *weights, const char *name, void *host_bytes, size_t bytes,
+                                      krea2_stream stream) {
+    clear_error();
+    KREA2_REQUIRE(weights && name && host_bytes, "weights_download: null argument");
+    auto it = weights->spans.find(name);
+    if (it == weights->spans.end()) return fail(KREA2_INVALID_ARGUMENT, "no span named %s", name);
+    KREA2_REQUIRE(bytes == it->second.bytes, "%s spans %zu bytes, got %zu", name, it->second.bytes, bytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    KREA2_CUDA(cudaMemcpyAsync(host_bytes, weights->base + it->second.offset, bytes, cudaMemcpyDeviceToHost, st));
+    KREA2_CUDA(cudaStreamSynchronize(st));
     return KREA2_OK;
 }
 
@@ -501,7 +523,7 @@ extern "C" int krea2_session_run(krea2_session *s, krea2_stream stream, uint16_t
             if (int status = run_profiled(s, first_block, count)) return status;
         } else {
             for (size_t i = first_block; i < first_block + count; i++)
-                if (int status = run_block(s, i, nullptr)) return status;
+                if (int status = run_block(s, s->stream, i, nullptr)) return status;
         }
         KREA2_CUDA(cudaMemcpyAsync(host_x, s->x, rows, cudaMemcpyDeviceToHost, s->stream));
         KREA2_CUDA(cudaStreamSynchronize(s->stream));

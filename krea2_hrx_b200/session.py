@@ -68,10 +68,7 @@ class Weights:
         """A host copy of one span (for tests that feed the same weights to the CPU oracle)."""
         ptr, n = self.locate(name)
         out = torch.empty(n // torch.empty((), dtype=dtype).element_size(), dtype=dtype)
-        torch.cuda.synchronize()
-        err = torch.cuda.cudart().cudaMemcpy(out.data_ptr(), ptr, n, 2)
-        if int(err) != 0:
-            raise RuntimeError(f"cudaMemcpy failed: {err}")
+        check(lib().krea2_weights_download(self._handle, name.encode(), out.data_ptr(), n, _stream_ptr(None)))
         return out
 
     def upload(self, name: str, host: torch.Tensor, stream=None) -> None:

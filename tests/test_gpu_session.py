@@ -1,0 +1,156 @@
+"""The resident session against the oracle chain, and the reference's session invariants
+(src/session/mod.rs:843-1065): graph replay equals the eager run after inputs change, a foreign
+stream is refused, a block range equals the chain of its parts."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import session_oracle as so
+
+pytestmark = pytest.mark.gpu
+
+k = pytest.importorskip("krea2_hrx_b200")
+
+
+def bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def small():
+    from krea2_hrx_b200 import session
+    dims = session.ModelDims(**so.SMALL)
+    stream = torch.cuda.current_stream()
+    weights = session.Weights(dims, 3)
+    weights.fill_synthetic(7, stream)
+    return dims, weights, so.host_weights(weights, 3)
+
+
+@pytest.mark.parametrize("tokens", [16, 275, 1043])
+def test_session_run_matches_the_oracle_chain(small, tokens):
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, tokens, 3)
+    assert (s.tokens(), s.layers()) == (tokens, 3)
+    x, mods, cos, sin = so.make_inputs(dims, tokens, 3, seed=tokens)
+    x_t = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    s.run(stream, x_t, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    want, trace = so.oracle_forward(dims, host, x, mods)
+    np.testing.assert_array_equal(bits(x_t), want)
+    # the last block's quantised operand is still in the session's buffers
+    ptr, n = s.buffer("a_s")
+    assert n >= tokens * 4
+    assert k.device_status() == 0
+    s.close()
+
+
+def test_synthetic_weights_follow_the_plan_layout(small):
+    """src/checkpoint/plan.rs:135-141: 256-byte aligned spans in name order; rows at the GEMM pitch
+    with zero padding; value ranges of the synthetic fill."""
+    dims, weights, host = small
+    from krea2_hrx_b200 import shape
+    names = sorted(f"blocks.{i}.{n}" for i in range(3) for n in
+                   ["qkvg.q", "qkvg.s", "wo.q", "wo.s", "gu.q", "gu.s", "down.q", "down.s", "prenorm", "postnorm",
+                    "qnorm", "knorm"])
+    base, _ = weights.locate(names[0])
+    cursor = base
+    for name in names:
+        ptr, n = weights.locate(name)
+        assert ptr == cursor and ptr % 256 == 0, name
+        cursor = ptr + -(-n // 256) * 256
+    down = host[0]["down.q"].reshape(dims.hidden, shape.gemm_pitch(dims.inter))
+    assert down.min() >= -127 and down.max() <= 127 and np.all(down[:, dims.inter:] == 0)
+    assert abs(float(down[:, :dims.inter].astype(np.float64).mean())) < 0.5
+    s = host[1]["gu.s"]
+    assert s.min() >= 1e-3 and s.max() <= 1e-2 + 1e-6
+    assert 0.05 < host[2]["prenorm"].std() < 0.2
+    with pytest.raises(k.InvalidArgument, match="no span named"):
+        weights.locate("blocks.9.qkvg.q")
+
+
+def test_graph_replay_equals_the_eager_run_after_inputs_change(small):
+    """src/session/mod.rs:915-973."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    tokens = 275
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, tokens, 3)
+    assert s.launches_per_forward() == 3 * 8
+    for seed in (1, 2, 1):
+        x, mods, cos, sin = so.make_inputs(dims, tokens, 3, seed=seed)
+        eager = torch.from_numpy(x.copy()).view(torch.bfloat16)
+        s.run(stream, eager, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+        # fresh device allocations every time: the graph must not depend on caller addresses
+        x_dev = torch.from_numpy(x.copy()).view(torch.bfloat16).cuda()
+        mods_dev = torch.from_numpy(mods).cuda()
+        s.run_device(stream, x_dev, mods_dev, torch.from_numpy(cos), torch.from_numpy(sin))
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(bits(x_dev), bits(eager))
+    s.close()
+
+
+def test_a_block_range_equals_the_chain_of_its_parts(small):
+    """src/session/mod.rs:1000-1065: two independent prefixes equal the whole."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    tokens = 64
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, tokens, 3)
+    x, mods, cos, sin = so.make_inputs(dims, tokens, 3, seed=4)
+    args = (torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    whole = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    s.run(stream, whole, *args)
+    parts = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    s.run(stream, parts, *args, first_block=0, block_count=2)
+    s.run(stream, parts, *args, first_block=2, block_count=1)
+    np.testing.assert_array_equal(bits(parts), bits(whole))
+    with pytest.raises(k.InvalidArgument, match="block range"):
+        s.run(stream, parts, *args, first_block=3)
+    with pytest.raises(k.InvalidArgument, match="block range"):
+        s.run(stream, parts, *args, first_block=1, block_count=3)
+    s.close()
+
+
+def test_a_session_refuses_a_foreign_stream_and_wrong_sizes(small):
+    """src/session/mod.rs:375-380, 975-998, 516-528."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, 32, 2)
+    x, mods, cos, sin = so.make_inputs(dims, 32, 2, seed=5)
+    x_t = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    other = torch.cuda.Stream()
+    with pytest.raises(k.InvalidArgument, match="stream that created it"):
+        s.run(other, x_t, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    with pytest.raises(k.InvalidArgument, match="x has"):
+        s.run(stream, x_t[:-1].clone(), torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    with pytest.raises(k.InvalidArgument, match="mods"):
+        s.run(stream, x_t, torch.from_numpy(mods[:1].copy()), torch.from_numpy(cos), torch.from_numpy(sin))
+    with pytest.raises(k.InvalidArgument, match="cos/sin"):
+        s.run(stream, x_t, torch.from_numpy(mods), torch.from_numpy(cos[:1].copy()), torch.from_numpy(sin))
+    with pytest.raises(k.InvalidArgument, match="weights hold"):
+        session.Session(stream, weights, 32, 4)
+    s.close()
+
+
+def test_profiled_forward_reports_the_reference_stage_labels(small):
+    """src/session/mod.rs:461-494, 627-647."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, 128, 3)
+    x, mods, cos, sin = so.make_inputs(dims, 128, 3, seed=6)
+    plain = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    s.run(stream, plain, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    assert s.set_profile(True) is False
+    profiled = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    s.run(stream, profiled, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    np.testing.assert_array_equal(bits(profiled), bits(plain))
+    table = dict(s.stage_profile())
+    for label in ["prepare", "gemm qkvg", "prepare gated", "gemm wo + residual", "gemm gate|up + swiglu",
+                  "prepare swiglu", "gemm down + residual"]:
+        assert table[label] > 0.0, label
+    assert s.set_profile(False) is True
+    s.close()
