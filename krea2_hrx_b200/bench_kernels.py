@@ -1,0 +1,157 @@
+"""Per-kernel timings of the W8A8 path, the counterpart of the reference's kernel bench
+(benches/kernels.rs:56-193: the four GEMMs over M in {1043, 4095, 4096, 4109, 12301, 16397}).
+
+    python -m krea2_hrx_b200.bench_kernels --kernel all --m 4608
+    python -m krea2_hrx_b200.bench_kernels --kernel gu --m 4608 --dims baseline --iters 20
+
+Each line of output is one JSON object: the kernel, its shape, the mean CUDA-event time of
+`iters` back-to-back launches after `warmup` (a 256 MB buffer is rewritten between timed
+launches when --flush-l2 is given; GEMM weights at these sizes exceed L2 anyway), and the
+rate against its roofline: integer TOP/s for GEMMs (2*M*N*K), algorithmic GB/s for prologues
+(one read of the 16-bit rows, one int8 row and one f32 scale written per token).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from krea2_hrx_b200 import ops, shape  # noqa: E402
+
+DIMS = {
+    # hidden, fused q|k|v|gate (or q|k|v) width, SwiGLU inner width
+    "reference": dict(hidden=6144, qkv=15360, inter=16384),  # src/session/mod.rs:35-45
+    "baseline": dict(hidden=3072, qkv=9216, inter=8192),     # the dimensions BASELINE.json words
+}
+REFERENCE_M = [1043, 4095, 4096, 4109, 12301, 16397]  # benches/kernels.rs:64
+
+
+def gemm_case(kind, dims):
+    h, qkv, inter = dims["hidden"], dims["qkv"], dims["inter"]
+    return {"qkvg": ("gemm_i8_256", h, qkv), "wo": ("gemm_i8_resid_256", h, h), "gu": ("gemm_i8_swiglu_256", h, 2 * inter),
+            "down": ("gemm_i8_resid_256x256", inter, h), "acc": ("gemm_i8_acc", h, qkv)}[kind]
+
+
+def time_launches(fn, iters, warmup, flush):
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    if flush:
+        total = 0.0
+        for _ in range(iters):
+            scratch.fill_(1)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            fn()
+            end.record(stream)
+            torch.cuda.synchronize()
+            total += start.elapsed_time(end)
+        return total / iters
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(iters):
+        fn()
+    end.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def run_gemm(kind, m, dims, iters, warmup, flush):
+    name, k, n = gemm_case(kind, dims)
+    pitch = shape.gemm_pitch(k)
+    gen = torch.Generator(device="cuda").manual_seed(m + n)
+    a = torch.randint(-127, 128, (m, pitch), generator=gen, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (n, pitch), generator=gen, device="cuda", dtype=torch.int8)
+    ws = torch.rand(n, generator=gen, device="cuda") * 9e-3 + 1e-3
+    a_scale = torch.rand(m, generator=gen, device="cuda") * 0.05 + 1e-3
+    gate = torch.randn(n, generator=gen, device="cuda") * 0.1
+    if name == "gemm_i8_256":
+        c = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        fn = lambda: ops.gemm_i8_256(m, a, w, ws, a_scale, c, k, pitch, n)
+    elif name == "gemm_i8_swiglu_256":
+        c = torch.empty((m, n // 2), dtype=torch.float16, device="cuda")
+        fn = lambda: ops.gemm_i8_swiglu_256(m, a, w, ws, a_scale, c, k, pitch, n)
+    elif name == "gemm_i8_resid_256":
+        c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops.gemm_i8_resid_256(m, a, w, ws, a_scale, c, gate, k, pitch, n)
+    elif name == "gemm_i8_resid_256x256":
+        c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops.gemm_i8_resid_256x256(m, a, w, ws, a_scale, c, gate, k, pitch, n, 4,
+                                               int(shape.gemm_schedule_rows(m)))
+    else:
+        c = torch.empty((m, n), dtype=torch.int32, device="cuda")
+        fn = lambda: ops.gemm_i8_acc(m, a, w, c, k, pitch, n)
+    ms = time_launches(fn, iters, warmup, flush)
+    gop = 2.0 * m * n * k / 1e9
+    return {"kernel": name, "stem": kind, "m": m, "k": k, "n": n, "k_stride": pitch, "ms": ms, "gop": gop,
+            "tops": gop / ms}
+
+
+def run_prologue(kind, m, dims, iters, warmup, flush):
+    h, qkv, inter = dims["hidden"], dims["qkv"], dims["inter"]
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    if kind == "norm":
+        width = h
+        x = torch.randn((m, width), generator=gen, device="cuda").to(torch.bfloat16)
+        vec = [torch.randn(width, generator=gen, device="cuda") * 0.1 for _ in range(3)]
+        bytes_in = 2 * width
+    elif kind == "gated":
+        width = h
+        x = torch.randn((m, width), generator=gen, device="cuda").to(torch.float16)
+        gate_stride = qkv if qkv % 256 == 0 and qkv >= 2 * width else width
+        gate = torch.randn((m, gate_stride), generator=gen, device="cuda").to(torch.float16)
+        bytes_in = 4 * width
+    else:
+        width = inter
+        x = torch.randn((m, width), generator=gen, device="cuda").to(torch.float16)
+        bytes_in = 2 * width
+    pitch = shape.gemm_pitch(width)
+    q = torch.zeros((m, pitch), dtype=torch.int8, device="cuda")
+    qs = torch.zeros(m, dtype=torch.float32, device="cuda")
+    if kind == "norm":
+        fn = lambda: ops.prepare_norm_i8(x, vec[0], vec[1], vec[2], q, qs, width, pitch, 1e-5)
+    elif kind == "gated":
+        offset = gate_stride - width
+        view = gate.view(-1)[offset:]
+        fn = lambda: ops.prepare_gated_i8(x, view, q, qs, width, pitch, gate_stride, tokens=m)
+    else:
+        fn = lambda: ops.prepare_plain_i8(x, q, qs, width, pitch)
+    ms = time_launches(fn, iters, warmup, flush)
+    nbytes = m * (bytes_in + width + 4)
+    return {"kernel": f"prepare_{kind}_i8", "m": m, "width": width, "out_stride": pitch, "ms": ms,
+            "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--kernel", default="all",
+                        help="qkvg, wo, gu, down, acc, norm, gated, plain, gemms, prologues or all (comma separated)")
+    parser.add_argument("--m", default="4608", help="rows, comma separated; 'reference' = the reference's bench list")
+    parser.add_argument("--dims", default="reference", choices=sorted(DIMS))
+    parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--flush-l2", action="store_true")
+    args = parser.parse_args()
+    kinds = []
+    for item in args.kernel.split(","):
+        kinds += {"all": ["qkvg", "wo", "gu", "down", "norm", "gated", "plain"], "gemms": ["qkvg", "wo", "gu", "down"],
+                  "prologues": ["norm", "gated", "plain"]}.get(item, [item])
+    rows = REFERENCE_M if args.m == "reference" else [int(v) for v in args.m.split(",")]
+    dims = DIMS[args.dims]
+    for kind in kinds:
+        for m in rows:
+            runner = run_prologue if kind in ("norm", "gated", "plain") else run_gemm
+            result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
+            result["dims"] = args.dims
+            print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -50,12 +50,12 @@ __device__ __forceinline__ float hf_round(float x) { return __half2float(__float
 // Cephes polynomial, scaling by two exact powers of two.  It stands in for the reference's
 // approximate `expf<afn>` (kernels/prepare_gated_i8.loom:99, gemm_i8_swiglu_256.loom:650).
 __device__ __forceinline__ float canonical_exp(float x) {
-    if (x != x) return x;
-    if (x > 88.72283935546875f) return __int_as_float(0x7f800000);
-    if (x < -104.0f) return 0.0f;
-    float t = __fmul_rn(x, 1.44269502162933349609375f);
+    // Clamped, not branched: above 89 the scaled result overflows to +inf by itself, below -104 it
+    // underflows to zero or the smallest subnormal; a NaN passes through.
+    float xc = fminf(fmaxf(x, -104.0f), 89.0f);
+    float t = __fmul_rn(xc, 1.44269502162933349609375f);
     float n = rintf(t);
-    float r = __fmaf_rn(n, -0.693359375f, x);
+    float r = __fmaf_rn(n, -0.693359375f, xc);
     r = __fmaf_rn(n, 2.12194440e-4f, r);
     float p = 1.9875691500e-4f;
     p = __fmaf_rn(p, r, 1.3981999507e-3f);
@@ -66,17 +66,18 @@ __device__ __forceinline__ float canonical_exp(float x) {
     float r2 = __fmul_rn(r, r);
     float y = __fmaf_rn(p, r2, r);
     y = __fadd_rn(y, 1.0f);
-    int ni = (int)n;
-    int h1 = ni / 2, h2 = ni - h1;
+    int ni = __float2int_rn(n);
+    int h1 = ni >> 1, h2 = ni - h1;  // floor(n/2) and the rest: both exponents stay in range
     float a = __int_as_float((h1 + 127) << 23);
     float b = __int_as_float((h2 + 127) << 23);
-    return __fmul_rn(__fmul_rn(y, a), b);
+    float result = __fmul_rn(__fmul_rn(y, a), b);
+    return x != x ? x : result;
 }
 
 // 1 / (1 + exp(0 - g)), unrounded f32 (kernels/prepare_gated_i8.loom:98-101).
 __device__ __forceinline__ float sigmoid_f32(float g) {
     float e = canonical_exp(__fsub_rn(0.0f, g));
-    return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+    return __frcp_rn(__fadd_rn(1.0f, e));  // the correctly rounded reciprocal equals the IEEE quotient 1 / den
 }
 
 #endif  // __CUDACC__

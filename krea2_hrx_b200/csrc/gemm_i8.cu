@@ -3,11 +3,11 @@
 //   krea2_gemm_i8_swiglu_256  (kernels/gemm_i8_*.loom), plus the raw-accumulator variant.
 //
 // One persistent, warp-specialised kernel, templated on the epilogue and the N tile:
-//   warp 4      TMA producer: int8 A [128 x 128B] and W [BN x 128B] tiles, 128-byte swizzle,
+//   warp 8      TMA producer: int8 A [128 x 128B] and W [BN x 128B] tiles, 128-byte swizzle,
 //               into a ring of shared-memory stages, completion on mbarriers
-//   warp 5      one thread issues tcgen05.mma kind::i8 (128 x BN x 32 per instruction),
+//   warp 9      one thread issues tcgen05.mma kind::i8 (128 x BN x 32 per instruction),
 //               accumulating i32 in tensor memory; tcgen05.commit frees the stage
-//   warps 0-3   epilogue: tcgen05.ld of the 128 x BN accumulator (one row per thread),
+//   warps 0-7   epilogue: tcgen05.ld of the 128 x BN accumulator (one row per thread),
 //               i32 -> f32, weight-channel and token scales, the bf16 rounding points of
 //               the reference and the residual / SwiGLU / plain store
 // Two accumulators alternate in tensor memory, so the epilogue of one tile runs under the
@@ -31,10 +31,10 @@ namespace {
 constexpr int kBlockM = 128;        // accumulator rows = TMEM lanes
 constexpr int kBlockK = 128;        // bytes of K per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 32;          // K of one kind::i8 instruction
-constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;   // two warps per 32-lane quarter of tensor memory, alternating column chunks
+constexpr int kProducerWarp = kEpilogueWarps;
+constexpr int kMmaWarp = kEpilogueWarps + 1;
+constexpr int kGemmThreads = (kEpilogueWarps + 2) * 32;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after two seconds
 
 enum class Epi { Plain, Resid, Swiglu, Acc };
@@ -371,7 +371,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // Epilogue warps 0..3: warp w reads TMEM lanes 32w..32w+31, one accumulator row per thread.
+        // Epilogue warps: warp w may read TMEM lanes 32*(w%4)..+31 only, one accumulator row per
+        // thread; the warps that share a quarter take alternate 32-column chunks.
+        constexpr int kColumnGroups = kEpilogueWarps / 4;
+        const int quarter = warp & 3, group = warp >> 2;
         uint32_t local = 0;
         for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, local++) {
             const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
@@ -379,13 +382,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
-            const uint32_t row = m0 + warp * 32 + lane;
+            const uint32_t row = m0 + quarter * 32 + lane;
             const bool in_range = row < g.m;
             float as = 0.0f;
             if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
-            const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(warp * 32) << 16);
+            const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = group; c < BN / 32; c += kColumnGroups) {
                 int32_t acc[32];
                 tmem_load_32(lane_base + c * 32, acc);
                 if (in_range) epilogue_chunk<E>(acc, g, row, n0 + c * 32, as);

@@ -46,36 +46,54 @@ __device__ __forceinline__ void unpack_f16(const uint4 &raw, float (&v)[8]) {
     }
 }
 
-// One radix-4 butterfly (kernels/prepare_norm_i8.loom:194-201).
-template <bool kHalf>
-__device__ __forceinline__ float stage_round(float x) {
-    if constexpr (kHalf) return hf_round(__fmul_rn(x, 0.25f));  // prepare_plain_i8.loom:120-127
-    return x;
+// bf16 rounding of two values with one packed conversion (cvt.rn.bf16x2.f32).
+__device__ __forceinline__ void bf_round2(float &a, float &b) {
+    __nv_bfloat162 packed = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<uint32_t *>(&packed);
+    a = __uint_as_float(u << 16);
+    b = __uint_as_float(u & 0xffff0000u);
 }
 
+// What each Hadamard stage does to its pair of outputs: nothing for the f32 rotation; a quarter
+// and an f16 rounding for the plain prologue (kernels/prepare_plain_i8.loom:120-127).
+template <bool kHalf>
+__device__ __forceinline__ void stage_round2(float &a, float &b) {
+    if constexpr (kHalf) {
+        const float2 f = __half22float2(__floats2half2_rn(__fmul_rn(a, 0.25f), __fmul_rn(b, 0.25f)));
+        a = f.x;
+        b = f.y;
+    }
+}
+
+// One radix-4 butterfly (kernels/prepare_norm_i8.loom:194-201).
 template <bool kHalf>
 __device__ __forceinline__ void butterfly(float &e0, float &e1, float &e2, float &e3) {
     float s01 = __fadd_rn(e0, e1), s23 = __fadd_rn(e2, e3);
     float d01 = __fsub_rn(e0, e1), d23 = __fsub_rn(e2, e3);
-    e0 = stage_round<kHalf>(__fadd_rn(s01, d23));
-    e1 = stage_round<kHalf>(__fsub_rn(s01, d23));
-    e2 = stage_round<kHalf>(__fadd_rn(d01, s23));
-    e3 = stage_round<kHalf>(__fsub_rn(s23, d01));
+    e0 = __fadd_rn(s01, d23);
+    e1 = __fsub_rn(s01, d23);
+    e2 = __fadd_rn(d01, s23);
+    e3 = __fsub_rn(s23, d01);
+    stage_round2<kHalf>(e0, e1);
+    stage_round2<kHalf>(e2, e3);
 }
 
-// A radix-4 stage whose four inputs sit in four lanes: lane bit `m1` picks e0/e1 (and e2/e3),
-// lane bit `m2` picks the pair.  Each lane forms the sum and difference of its pair, swaps
-// differences with the other pair, and ends with the output that belongs at its position.
+// A radix-4 stage whose four inputs e0..e3 sit in four lanes: lane bit `m1` separates e0|e1
+// (and e2|e3), lane bit `m2` separates the pairs.  Every lane forms s = own + partner and
+// d = own - partner with its m1 partner, then adds the d of its m2 partner.  For the lanes
+// holding e1 and e3, d is the negated pair difference, which is exactly the sign the outputs
+// o1 = s01 - d23 and o3 = s23 - d01 want, so one formula serves all four lanes.
 template <bool kHalf>
-__device__ __forceinline__ void cross_stage(float (&v)[8], int lane, int m1, int m2) {
-    const bool second = (lane & m1) != 0;
+__device__ __forceinline__ void cross_stage(float (&v)[8], int m1, int m2) {
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-        float p = __shfl_xor_sync(kFull, v[e], m1);
-        float s = __fadd_rn(v[e], p);
-        float d = second ? __fsub_rn(p, v[e]) : __fsub_rn(v[e], p);
-        float dp = __shfl_xor_sync(kFull, d, m2);
-        v[e] = stage_round<kHalf>(second ? __fsub_rn(s, dp) : __fadd_rn(s, dp));
+    for (int e = 0; e < 8; e += 2) {
+        float p0 = __shfl_xor_sync(kFull, v[e], m1), p1 = __shfl_xor_sync(kFull, v[e + 1], m1);
+        float s0 = __fadd_rn(v[e], p0), s1 = __fadd_rn(v[e + 1], p1);
+        float d0 = __fsub_rn(v[e], p0), d1 = __fsub_rn(v[e + 1], p1);
+        float q0 = __shfl_xor_sync(kFull, d0, m2), q1 = __shfl_xor_sync(kFull, d1, m2);
+        v[e] = __fadd_rn(s0, q0);
+        v[e + 1] = __fadd_rn(s1, q1);
+        stage_round2<kHalf>(v[e], v[e + 1]);
     }
 }
 
@@ -83,7 +101,7 @@ __device__ __forceinline__ void cross_stage(float (&v)[8], int lane, int m1, int
 // 1, 4, 16, 64 (kernels/prepare_norm_i8.loom:174-309; prepare_plain_i8.loom:82-279 with the
 // f16 rounding after every stage).
 template <bool kHalf>
-__device__ __forceinline__ void hadamard256(float (&v)[8], int lane) {
+__device__ __forceinline__ void hadamard256(float (&v)[8]) {
     butterfly<kHalf>(v[0], v[1], v[2], v[3]);
     butterfly<kHalf>(v[4], v[5], v[6], v[7]);
     // stride 4: e0, e1 = v[c], v[c+4] of the even lane; e2, e3 = the same of the odd lane.
@@ -92,11 +110,24 @@ __device__ __forceinline__ void hadamard256(float (&v)[8], int lane) {
         float s = __fadd_rn(v[c], v[c + 4]);
         float d = __fsub_rn(v[c], v[c + 4]);
         float dp = __shfl_xor_sync(kFull, d, 1);
-        v[c] = stage_round<kHalf>(__fadd_rn(s, dp));
-        v[c + 4] = stage_round<kHalf>(__fsub_rn(s, dp));
+        v[c] = __fadd_rn(s, dp);
+        v[c + 4] = __fsub_rn(s, dp);
+        stage_round2<kHalf>(v[c], v[c + 4]);
     }
-    cross_stage<kHalf>(v, lane, 2, 4);
-    cross_stage<kHalf>(v, lane, 8, 16);
+    cross_stage<kHalf>(v, 2, 4);
+    cross_stage<kHalf>(v, 8, 16);
+}
+
+// Four i32 to four saturated int8, first value in the low byte.
+__device__ __forceinline__ uint32_t pack_s8x4(int x0, int x1, int x2, int x3) {
+    uint32_t out;
+    asm("{ .reg .u32 hi;\n"
+        "cvt.pack.sat.s8.s32.b32 hi, %4, %3, 0;\n"
+        "cvt.pack.sat.s8.s32.b32 %0, %2, %1, hi;\n"
+        "}"
+        : "=r"(out)
+        : "r"(x0), "r"(x1), "r"(x2), "r"(x3));
+    return out;
 }
 
 __device__ __forceinline__ float block_max(float value, float *scratch, int lane, int warp) {
@@ -128,14 +159,13 @@ __device__ __forceinline__ void quantise_and_store(float (&v)[CPL][8], float rot
     float inv = __fdiv_rn(rotation, s);
 #pragma unroll
     for (int j = 0; j < CPL; j++) {
-        uint32_t word[2] = {0u, 0u};
+        // max(x, -127) before rounding equals the clamp after it (-127 is an integer) and sends a
+        // NaN to -127 as the reference's maxnum does; the saturating pack clamps at +127.
+        int code[8];
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            float f = rintf(__fmul_rn(v[j][e], inv));
-            f = fminf(fmaxf(f, -127.0f), 127.0f);
-            word[e >> 2] |= (static_cast<uint32_t>(static_cast<int>(f)) & 0xffu) << (8 * (e & 3));
-        }
-        *reinterpret_cast<uint2 *>(q_row + 8 * (j * kThreads + t)) = make_uint2(word[0], word[1]);
+        for (int e = 0; e < 8; e++) code[e] = __float2int_rn(fmaxf(__fmul_rn(v[j][e], inv), -127.0f));
+        *reinterpret_cast<uint2 *>(q_row + 8 * (j * kThreads + t)) =
+            make_uint2(pack_s8x4(code[0], code[1], code[2], code[3]), pack_s8x4(code[4], code[5], code[6], code[7]));
     }
     if (t == 0) q_scale[row] = s;
 }
@@ -160,7 +190,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     for (int j = 0; j < CPL; j++) {
         unpack_bf16(raw[j], v[j]);
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] = __fadd_rn(acc[e], __fmul_rn(v[j][e], v[j][e]));
+        for (int e = 0; e < 8; e++) acc[e] = __fmaf_rn(v[j][e], v[j][e], acc[e]);  // the square of a bf16 is exact in f32
     }
     // 8-wide fold, then the wave by xor butterfly, then the eight waves in the reference's
     // written order (kernels/prepare_norm_i8.loom:101-138).
@@ -185,15 +215,22 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
         *reinterpret_cast<float4 *>(sh) = __ldg(reinterpret_cast<const float4 *>(mod_shift + base));
         *reinterpret_cast<float4 *>(sh + 4) = __ldg(reinterpret_cast<const float4 *>(mod_shift + base + 4));
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
+        for (int e = 0; e < 8; e += 2) {
             // :152-168: bf16 after the norm scale, bf16 of (1 + mod_scale), bf16 of the product,
             // bf16 after the shift.
-            float normed = bf_round(__fmul_rn(__fmul_rn(v[j][e], rinv), __fadd_rn(ns[e], 1.0f)));
-            float ms1 = bf_round(__fadd_rn(ms[e], 1.0f));
-            float scaled = bf_round(__fmul_rn(normed, ms1));
-            v[j][e] = bf_round(__fadd_rn(scaled, sh[e]));
+            float n0 = __fmul_rn(__fmul_rn(v[j][e], rinv), __fadd_rn(ns[e], 1.0f));
+            float n1 = __fmul_rn(__fmul_rn(v[j][e + 1], rinv), __fadd_rn(ns[e + 1], 1.0f));
+            bf_round2(n0, n1);
+            float m0 = __fadd_rn(ms[e], 1.0f), m1 = __fadd_rn(ms[e + 1], 1.0f);
+            bf_round2(m0, m1);
+            float s0 = __fmul_rn(n0, m0), s1 = __fmul_rn(n1, m1);
+            bf_round2(s0, s1);
+            float o0 = __fadd_rn(s0, sh[e]), o1 = __fadd_rn(s1, sh[e + 1]);
+            bf_round2(o0, o1);
+            v[j][e] = o0;
+            v[j][e + 1] = o1;
         }
-        hadamard256<false>(v[j], lane);
+        hadamard256<false>(v[j]);
     }
     quantise_and_store<CPL>(v, 0.0625f, q + row * out_stride, q_scale, row, wave_max, t);
 }
@@ -222,13 +259,18 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
         unpack_f16(a_raw[j], v[j]);
         unpack_f16(g_raw[j], g);
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
+        for (int e = 0; e < 8; e += 2) {
             // kernels/prepare_gated_i8.loom:94-106
-            float a = bf_round(v[j][e]);
-            float sig = bf_round(sigmoid_f32(g[e]));
-            v[j][e] = bf_round(__fmul_rn(a, sig));
+            float a0 = v[j][e], a1 = v[j][e + 1];
+            bf_round2(a0, a1);
+            float g0 = sigmoid_f32(g[e]), g1 = sigmoid_f32(g[e + 1]);
+            bf_round2(g0, g1);
+            float o0 = __fmul_rn(a0, g0), o1 = __fmul_rn(a1, g1);
+            bf_round2(o0, o1);
+            v[j][e] = o0;
+            v[j][e + 1] = o1;
         }
-        hadamard256<false>(v[j], lane);
+        hadamard256<false>(v[j]);
     }
     quantise_and_store<CPL>(v, 0.0625f, q + row * out_stride, q_scale, row, wave_max, t);
 }
@@ -249,7 +291,7 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
 #pragma unroll
     for (int j = 0; j < CPL; j++) {
         unpack_f16(raw[j], v[j]);
-        hadamard256<true>(v[j], lane);
+        hadamard256<true>(v[j]);
     }
     quantise_and_store<CPL>(v, 16.0f, q + row * out_stride, q_scale, row, wave_max, t);
 }

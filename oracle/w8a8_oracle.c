@@ -89,14 +89,15 @@ void oracle_f32_to_bf16(const float *src, uint16_t *dst, size_t n) { for (size_t
  * The canonical replacement: Cody-Waite reduction by ln2 in two pieces and the
  * classic degree-6 minimax polynomial (the published Cephes expf), every step a
  * single f32 operation or a fused multiply-add, so that a CPU and a GPU produce the
- * same bits.  Accurate to about 1 ulp; callers round the result to bf16 right away. */
+ * same bits.  Accurate to about 1 ulp; callers round the result to bf16 right away.
+ * The quotient 1/(1+e) that follows is a correctly rounded reciprocal. */
 float oracle_exp(float x) {
-    if (x != x) return x;
-    if (x > 88.72283935546875f) return INFINITY;
-    if (x < -104.0f) return 0.0f;
-    float t = x * 1.44269502162933349609375f;
+    /* Clamped, not branched: above 89 the scaled result overflows to +inf by itself, below
+     * -104 it underflows to zero or the smallest subnormal; a NaN passes through. */
+    float xc = fminf(fmaxf(x, -104.0f), 89.0f);
+    float t = xc * 1.44269502162933349609375f;
     float n = rintf(t);
-    float r = fmaf(n, -0.693359375f, x);
+    float r = fmaf(n, -0.693359375f, xc);
     r = fmaf(n, 2.12194440e-4f, r);
     float p = 1.9875691500e-4f;
     p = fmaf(p, r, 1.3981999507e-3f);
@@ -108,10 +109,11 @@ float oracle_exp(float x) {
     float y = fmaf(p, r2, r);
     y = y + 1.0f;
     int ni = (int)n;
-    int h1 = ni / 2, h2 = ni - h1;
+    int h1 = ni >> 1, h2 = ni - h1; /* floor(n/2) and the rest: both exponents stay in range */
     float a = bits_f32((uint32_t)(h1 + 127) << 23);
     float b = bits_f32((uint32_t)(h2 + 127) << 23);
-    return (y * a) * b;
+    float result = (y * a) * b;
+    return x != x ? x : result;
 }
 
 /* sigma(g) = 1 / (1 + exp(0 - g)) in f32, unrounded (kernels/prepare_gated_i8.loom:98-101). */
