@@ -18,6 +18,7 @@
 // producer drains its loads in flight, tensor memory is released and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -134,6 +135,64 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, int32_t (&r)[32])
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(address));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- two-CTA (cta_group::2) forms: a pair of CTAs in one cluster drives both SMs' tensor cores
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of `p` (an address in this CTA's shared memory) inside CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+// TMA tile load whose completion is counted on a barrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, uint32_t bar_cluster_address,
+                                                 int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(bar_cluster_address), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *dst, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives, once the MMAs issued so far have completed, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    const uint16_t both = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(both)
+        : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte
@@ -407,6 +466,166 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------- two-CTA kernel
+// A cluster of two CTAs computes a 256 x 256 tile: CTA r holds rows r*128.. of A and rows
+// r*128.. of the W tile in its own shared memory (32 KB per stage instead of 48), the leader's
+// MMA thread issues tcgen05.mma.cta_group::2 (256 x 256 x 32) that reads both halves, and each
+// CTA ends up with its 128 accumulator rows x 256 columns in its own tensor memory.  Per SM this
+// moves a third less operand data than the single-CTA tile and leaves six stages in flight.
+// Barriers: each CTA's loads complete on the LEADER's full[s]; the leader's commit arrives on
+// empty[s] and acc_full[a] of both CTAs; one lane per epilogue warp of both CTAs arrives on the
+// leader's acc_empty[a].
+struct PairTile {
+    static constexpr int kStages = 6;
+    static constexpr int kBN = 256;
+    static constexpr int kABytes = kBlockM * kBlockK;
+    static constexpr int kBBytes = (kBN / 2) * kBlockK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemColumns = 2 * kBN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <Epi E>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const GemmArgs g) {
+    using T = PairTile;
+    constexpr int BN = T::kBN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + T::kStages * T::kStageBytes);
+    uint64_t *empty = full + T::kStages;
+    uint64_t *acc_full = empty + T::kStages;
+    uint64_t *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t m_tiles = (g.m + 2 * kBlockM - 1) / (2 * kBlockM);
+    const uint32_t tiles = m_tiles * (g.n / BN);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::kStages; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(acc_full + a, 1);
+            mbar_init(acc_empty + a, 2 * kEpilogueWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tmem_alloc_pair(tmem_slot, T::kTmemColumns);
+    }
+    tc_fence_before();
+    cluster_sync_all();  // barriers of both CTAs are initialised and the allocation is visible
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kProducerWarp) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (uint32_t tile = pair; alive && tile < tiles; tile += pairs) {
+                const int m0 = static_cast<int>((tile % m_tiles) * 2 * kBlockM + rank * kBlockM);
+                const int n0 = static_cast<int>((tile / m_tiles) * BN + rank * (BN / 2));
+                for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
+                    if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, kProducerTimedOut)) {
+                        alive = false;
+                        break;
+                    }
+                    uint8_t *a_dst = smem + stage * T::kStageBytes;
+                    const uint32_t leader_full = map_to_cta(full + stage, 0);
+                    if (leader) mbar_expect_tx(full + stage, 2 * T::kStageBytes);
+                    tma_load_2d_pair(a_dst, &map_a, leader_full, static_cast<int>(kb) * kBlockK, m0);
+                    tma_load_2d_pair(a_dst + T::kABytes, &map_w, leader_full, static_cast<int>(kb) * kBlockK, n0);
+                    if (++stage == T::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (*abort_flag) {
+                // Give loads still in flight time to land before this CTA can exit.
+                const uint64_t start = global_timer_ns();
+                while (global_timer_ns() - start < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = instruction_descriptor(2 * kBlockM, BN);
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool alive = true;
+            for (uint32_t tile = pair; alive && tile < tiles; tile += pairs, local++) {
+                const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
+                if (!mbar_wait(acc_empty + a, a_phase ^ 1u, abort_flag, kMmaTimedOut)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + a * BN;
+                for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
+                    if (!mbar_wait(full + stage, phase, abort_flag, kMmaTimedOut)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * T::kStageBytes);
+                    const uint64_t a_desc = smem_descriptor(a_addr);
+                    const uint64_t b_desc = smem_descriptor(a_addr + T::kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; k++)
+                        umma_i8_pair(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(empty + stage);
+                    if (++stage == T::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (alive) umma_commit_pair(acc_full + a);
+            }
+        }
+    } else {
+        constexpr int kColumnGroups = kEpilogueWarps / 4;
+        const int quarter = warp & 3, group = warp >> 2;
+        uint32_t local = 0;
+        for (uint32_t tile = pair; tile < tiles; tile += pairs, local++) {
+            const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
+            const uint32_t m0 = (tile % m_tiles) * 2 * kBlockM + rank * kBlockM, n0 = (tile / m_tiles) * BN;
+            const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            tc_fence_after();
+            const uint32_t row = m0 + quarter * 32 + lane;
+            const bool in_range = row < g.m;
+            float as = 0.0f;
+            if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
+            const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = group; c < BN / 32; c += kColumnGroups) {
+                int32_t acc[32];
+                tmem_load_32(lane_base + c * 32, acc);
+                if (in_range) epilogue_chunk<E>(acc, g, row, n0 + c * 32, as);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty + a, 0));
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still use it
+    tc_fence_after();
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, T::kTmemColumns);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -482,6 +701,62 @@ int launch_instance(cudaStream_t stream, const CUtensorMap &map_a, const CUtenso
     return KREA2_OK;
 }
 
+// Shared-memory limit and the number of two-CTA clusters this device can hold at once.
+template <Epi E>
+int ensure_pair_instance(int *clusters) {
+    static std::once_flag once[64];
+    static cudaError_t attr_status[64];
+    static int max_clusters[64];
+    int device = 0;
+    KREA2_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
+    std::call_once(once[device], [&] {
+        attr_status[device] = cudaFuncSetAttribute(gemm_i8_pair_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   PairTile::kSmemBytes);
+        if (attr_status[device] != cudaSuccess) return;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(2 * static_cast<unsigned>(sm_count()), 1, 1);
+        config.blockDim = dim3(kGemmThreads, 1, 1);
+        config.dynamicSmemBytes = PairTile::kSmemBytes;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 2;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        int n = 0;
+        attr_status[device] = cudaOccupancyMaxActiveClusters(&n, gemm_i8_pair_kernel<E>, &config);
+        max_clusters[device] = n;
+    });
+    if (attr_status[device] != cudaSuccess)
+        return fail(KREA2_RUNTIME, "cannot prepare the two-CTA GEMM: %s", cudaGetErrorString(attr_status[device]));
+    if (max_clusters[device] < 1) return fail(KREA2_RUNTIME, "this device cannot hold a two-CTA cluster of the GEMM");
+    *clusters = max_clusters[device];
+    return KREA2_OK;
+}
+
+template <Epi E>
+int launch_pair(cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_w, const GemmArgs &args) {
+    int clusters = 0;
+    if (int status = ensure_pair_instance<E>(&clusters)) return status;
+    const uint32_t tiles = ((args.m + 2 * kBlockM - 1) / (2 * kBlockM)) * (args.n / PairTile::kBN);
+    const unsigned pairs = tiles < static_cast<uint32_t>(clusters) ? tiles : static_cast<unsigned>(clusters);
+    gemm_i8_pair_kernel<E><<<2 * pairs, kGemmThreads, PairTile::kSmemBytes, stream>>>(map_a, map_w, args);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 (two-CTA) launch failed: %s", cudaGetErrorString(status));
+    return KREA2_OK;
+}
+
+// KREA2_GEMM_PAIR=0 keeps every launch on the single-CTA kernel (for A/B measurements).
+bool pair_enabled() {
+    static const bool enabled = [] {
+        const char *v = getenv("KREA2_GEMM_PAIR");
+        return !(v && v[0] == '0');
+    }();
+    return enabled;
+}
+
 // The `config.decl` ranges of the GEMM kernels (kernels/gemm_i8_256.loom:14-22,
 // gemm_i8_resid_256x256.loom:16-27) and the row-count bound (:97).
 int check_gemm(const char *name, size_t m, size_t k_size, size_t k_stride, size_t n_size, size_t m_group,
@@ -517,9 +792,12 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.gate = gate;
     args.c = c;
     const bool wide = n_size % 256 == 0;
+    // The two-CTA kernel wants whole 256-column tiles and more than one 128-row half to fill.
+    const bool pair = wide && m > kBlockM && pair_enabled();
     CUtensorMap map_a, map_w;
     if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
-    if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, wide ? 256 : 128)) return status;
+    if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, (wide && !pair) ? 256 : 128)) return status;
+    if (pair) return launch_pair<E>(stream, map_a, map_w, args);
     return wide ? launch_instance<E, 256>(stream, map_a, map_w, args)
                 : launch_instance<E, 128>(stream, map_a, map_w, args);
 }
@@ -539,6 +817,11 @@ int prepare_gemm_device() {
     if (int s = ensure_instance<Epi::Swiglu, 256>()) return s;
     if (int s = ensure_instance<Epi::Acc, 128>()) return s;
     if (int s = ensure_instance<Epi::Acc, 256>()) return s;
+    int clusters = 0;
+    if (int s = ensure_pair_instance<Epi::Plain>(&clusters)) return s;
+    if (int s = ensure_pair_instance<Epi::Resid>(&clusters)) return s;
+    if (int s = ensure_pair_instance<Epi::Swiglu>(&clusters)) return s;
+    if (int s = ensure_pair_instance<Epi::Acc>(&clusters)) return s;
     return KREA2_OK;
 }
 

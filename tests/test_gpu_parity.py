@@ -373,3 +373,17 @@ def test_unaligned_buffers_are_refused(ops):
     c = torch.zeros((1, 128), dtype=torch.float16, device="cuda")
     with pytest.raises(k.InvalidArgument, match="16-byte aligned"):
         ops.gemm_i8_256(1, a[1:129], w, s, s, c, 128, 128, 128)
+
+
+def test_single_cta_kernel_serves_the_same_shapes():
+    """Shapes with whole 256-column tiles and more than 128 rows go to the two-CTA kernel; with
+    KREA2_GEMM_PAIR=0 the same cases run on the single-CTA kernel and must give the same bits."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("KREA2_GEMM_PAIR") == "0":
+        pytest.skip("already the single-CTA run")
+    env = dict(os.environ, KREA2_GEMM_PAIR="0")
+    result = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k",
+                             "seeded_operands or integer_gemms or full_size"], env=env, capture_output=True, text=True)
+    assert result.returncode == 0, result.stdout[-2000:] + result.stderr[-2000:]
