@@ -106,6 +106,16 @@ int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *
  * reverse = 1: bf16 -> f16, reverse = 2: f16 -> bf16). */
 int krea2_lora_transport(krea2_stream stream, size_t elements, const void *src, void *dst, int reverse);
 
+/* Quantized::forward (src/training/quantized.rs:51-112) as one call: x bf16 [rows][inputs] ->
+ * out bf16 [rows][outputs] through the transport, prepare_plain_i8, gemm_i8_256 and the transport
+ * back; weight int8 [outputs][gemm_pitch(inputs)], scales f32 [outputs].  The four intermediates
+ * the reference takes from its buffer pool (:55-58) live in `workspace`, a device buffer of at
+ * least krea2_quantized_workspace_bytes(rows, inputs, outputs) bytes. */
+size_t krea2_quantized_workspace_bytes(size_t rows, size_t inputs, size_t outputs);
+int krea2_quantized_forward(krea2_stream stream, size_t rows, const void *x, const void *weight,
+                            const float *scales, void *out, size_t inputs, size_t outputs, void *workspace,
+                            size_t workspace_bytes);
+
 /* ---------------------------------------------------------------- generic dispatch
  * Ops::launch (src/ops/mod.rs:673-693): kernel by stem, config keys by name, packed
  * scalars, buffers in binding order, and the launch geometry the reference would use

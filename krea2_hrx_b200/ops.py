@@ -121,6 +121,20 @@ class Quantized:
         self.weight[:, :inputs] = weight.to(device)
         self.scales = scales.to(device).contiguous()
 
+    def forward_fused(self, stream, x: torch.Tensor, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The same projection through krea2_quantized_forward: one C call, intermediates in a
+        caller-owned workspace (allocated here when none is passed)."""
+        if x.shape[-1] != self.inputs or x.dtype != torch.bfloat16:
+            raise InvalidArgument("ConvRot projection dimensions")
+        rows = x.shape[0]
+        need = lib().krea2_quantized_workspace_bytes(rows, self.inputs, self.outputs)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        out = torch.empty((rows, self.outputs), dtype=torch.bfloat16, device=x.device)
+        check(lib().krea2_quantized_forward(_stream_ptr(stream), rows, _ptr(x), _ptr(self.weight), _ptr(self.scales),
+                                            _ptr(out), self.inputs, self.outputs, _ptr(workspace), _bytes(workspace)))
+        return out
+
     def forward(self, ops: Ops, stream, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.inputs or x.dtype != torch.bfloat16:
             raise InvalidArgument("ConvRot projection dimensions")

@@ -387,3 +387,18 @@ def test_single_cta_kernel_serves_the_same_shapes():
     result = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k",
                              "seeded_operands or integer_gemms or full_size"], env=env, capture_output=True, text=True)
     assert result.returncode == 0, result.stdout[-2000:] + result.stderr[-2000:]
+
+
+@pytest.mark.parametrize("inputs", [6144, 16384])
+def test_fused_convrot_call_equals_the_launch_sequence(ops, inputs):
+    """krea2_quantized_forward against the four Ops.launch calls and the reference's CPU algebra."""
+    weights, scales, x_bf16 = kat.convrot_case(inputs)
+    layer = ops.Quantized(torch.from_numpy(weights), torch.from_numpy(scales), weights.shape[0], inputs)
+    x = dev(x_bf16, torch.bfloat16)
+    stream = torch.cuda.current_stream()
+    fused = layer.forward_fused(stream, x)
+    np.testing.assert_array_equal(host(fused, np.uint16), kat.convrot_expected(weights, scales, x_bf16))
+    np.testing.assert_array_equal(host(fused, np.uint16), host(layer.forward(ops.Ops(), stream, x), np.uint16))
+    small = torch.empty(16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(k.InvalidArgument, match="workspace"):
+        layer.forward_fused(stream, x, small)
