@@ -39,8 +39,8 @@ DIMS = {  # hidden, kv_heads, head_dim, inter
 NOMINAL_INT8_TOPS = 4500.0  # dense int8 tensor peak of a B200, vendor figure
 
 # DRAM bytes (read + write) of one gate|up GEMM launch at M=4608, from the ncu capture summarised
-# in profiles/; None until a capture exists.
-GU_GEMM_DRAM_BYTES_PER_LAUNCH = None
+# in profiles/gemm_i8_pair_kernel_qkvg_gateup_m4608.md (algorithmic bytes A + W + C: 380.6 MB).
+GU_GEMM_DRAM_BYTES_PER_LAUNCH = 371.6e6
 
 
 def gemm_shapes(dims, tokens):

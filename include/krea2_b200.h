@@ -116,6 +116,25 @@ int krea2_quantized_forward(krea2_stream stream, size_t rows, const void *x, con
                             const float *scales, void *out, size_t inputs, size_t outputs, void *workspace,
                             size_t workspace_bytes);
 
+/* The same projection for callers that must not allocate.  No counterpart in the reference.
+ * Some hosts cannot hand this library a workspace: a plugin inside an engine that froze its
+ * device-memory arena at start-up, a serving loop whose allocator must not be entered on the
+ * request path, code that runs where cudaMalloc would synchronise or fail.  For them the four
+ * intermediates live in a 4 MiB array that is part of the library image (every GPU that loads
+ * the library carries it until the process exits), so this call needs nothing but its inputs
+ * and outputs and itself performs no cudaMalloc, cudaFree or other allocating call.
+ *  - Limit: krea2_quantized_workspace_bytes(rows, inputs, outputs) must not exceed
+ *    krea2_quantized_static_workspace_bytes() (4 MiB; e.g. 64 rows of 6144 -> 6144, 16 rows of
+ *    16384 -> 6144).  Larger calls are refused with KREA2_INVALID_ARGUMENT.
+ *  - The first call on each device resolves the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's bytes.  Every
+ *    byte that is read is written earlier in the same call, so nothing needs clearing; but two
+ *    calls that overlap on the GPU (different streams, or graph branches) race on it. */
+size_t krea2_quantized_static_workspace_bytes(void);
+int krea2_quantized_forward_static(krea2_stream stream, size_t rows, const void *x, const void *weight,
+                                   const float *scales, void *out, size_t inputs, size_t outputs);
+
 /* ---------------------------------------------------------------- generic dispatch
  * Ops::launch (src/ops/mod.rs:673-693): kernel by stem, config keys by name, packed
  * scalars, buffers in binding order, and the launch geometry the reference would use

@@ -76,6 +76,9 @@ SIGNATURES = {
     "krea2_quantized_workspace_bytes": (c_size_t, [c_size_t, c_size_t, c_size_t]),
     "krea2_quantized_forward": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,
                                         c_void_p, c_size_t]),
+    "krea2_quantized_static_workspace_bytes": (c_size_t, []),
+    "krea2_quantized_forward_static": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                               c_size_t]),
     "krea2_launch": (c_int, [c_void_p, c_char_p, POINTER(ConfigEntry), c_size_t, POINTER(c_uint64), c_size_t,
                              POINTER(Binding), c_size_t, c_size_t, c_size_t, c_uint32]),
     "krea2_shape_tokens_min": (c_size_t, []),

@@ -2,10 +2,22 @@
 // (src/training/quantized.rs:51-112) as one call: bf16 -> f16 transport, prepare_plain_i8,
 // gemm_i8_256, f16 -> bf16.  The four intermediates the reference takes from its buffer pool
 // (:55-58) live in a workspace the caller passes.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace krea2 {
 namespace {
+
+// Workspace of krea2_quantized_forward_static: part of the library image, so every GPU that
+// loads the library carries these 4 MiB until the process exits.  In host code this name is only
+// a handle for cudaGetSymbolAddress; the device address it resolves to is what kernels receive.
+constexpr size_t kStaticWorkspaceBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+
+// Never launched.  It names the array in device code so that the device image keeps it even
+// though every other use goes through cudaGetSymbolAddress on the host.
+__global__ void static_workspace_anchor(unsigned char **out) { *out = g_static_workspace; }
 
 size_t align256(size_t n) { return (n + 255) / 256 * 256; }
 
@@ -72,4 +84,38 @@ extern "C" int krea2_quantized_forward(krea2_stream stream, size_t rows, const v
                   "quantized_forward: the workspace spans %zu bytes, %zu are needed", workspace_bytes, need);
     return quantized_forward_in(static_cast<cudaStream_t>(stream), rows, x, weight, scales, out, inputs, outputs,
                                 static_cast<uint8_t *>(workspace));
+}
+
+extern "C" size_t krea2_quantized_static_workspace_bytes(void) { return kStaticWorkspaceBytes; }
+
+extern "C" int krea2_quantized_forward_static(krea2_stream stream, size_t rows, const void *x, const void *weight,
+                                              const float *scales, void *out, size_t inputs, size_t outputs) {
+    clear_error();
+    if (int s = check_quantized(rows, x, weight, scales, out, inputs, outputs)) return s;
+    const size_t need = workspace_layout(rows, inputs, outputs).total;
+    KREA2_REQUIRE(need <= kStaticWorkspaceBytes,
+                  "quantized_forward_static: %zu rows of %zu -> %zu need %zu bytes of scratch, the built-in "
+                  "workspace holds %zu; use krea2_quantized_forward with a caller workspace",
+                  rows, inputs, outputs, need, kStaticWorkspaceBytes);
+    // Per device, once, with that device current: resolve the device address of the array.
+    static std::mutex lock;
+    static uint8_t *address[64] = {nullptr};
+    int device = 0;
+    KREA2_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
+    uint8_t *workspace = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (!address[device]) {
+            void *resolved = nullptr;
+            cudaError_t status = cudaGetSymbolAddress(&resolved, g_static_workspace);
+            if (status != cudaSuccess)
+                return fail(KREA2_RUNTIME, "cudaGetSymbolAddress failed for the built-in workspace: %s",
+                            cudaGetErrorString(status));
+            address[device] = static_cast<uint8_t *>(resolved);
+        }
+        workspace = address[device];
+    }
+    return quantized_forward_in(static_cast<cudaStream_t>(stream), rows, x, weight, scales, out, inputs, outputs,
+                                workspace);
 }
