@@ -102,6 +102,36 @@ int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const void *a, const
 int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
                       size_t k_size, size_t k_stride, size_t n_size);
 
+/* ---------------------------------------------------------------- column-sharded GEMMs
+ * New with this library (the reference runs on one device).  Device r of `world` holds rows
+ * [r*N/world, (r+1)*N/world) of a weight and its scales, computes the matching column slab of
+ * the output and stores every finished vector straight into ALL devices' copies of the full
+ * output tensor through peer-mapped pointers, so the all-gather rides in the epilogue's stores
+ * over NVLink instead of following as a separate collective.  Each output element is still one
+ * full-K dot product of one CTA, so sharded results are bit-identical to the single-device ones.
+ * When the last CTA of a launch has finished, slot `rank` of every destination's flag array is
+ * set to `epoch`; krea2_shard_wait makes a stream wait (bounded, 2 s, then the device status
+ * word is raised) until all `world` slots of the local array have reached `epoch`. */
+typedef struct krea2_shard {
+    uint32_t world;     /* destination buffers, 1..8 */
+    uint32_t rank;      /* this launch's flag slot; dest[rank] is this device's own buffer (and the
+                           source of the residual for the resid kind) */
+    void *dest[8];      /* every device's copy of the full output [m][pitch], 16-bit elements */
+    size_t pitch;       /* elements per row of the full output (N, or N/2 for swiglu) */
+    size_t offset;      /* first output column of this shard; multiple of 16 */
+    uint32_t *flags[8]; /* per destination, `world` u32 slots; NULL entries are not signalled */
+    uint32_t epoch;     /* value published when this launch's stores are complete */
+    uint32_t *counter;  /* u32 on this device, zero before the first launch (the kernel re-zeroes it) */
+} krea2_shard;
+
+enum { KREA2_SHARD_PLAIN = 0, KREA2_SHARD_RESID = 1, KREA2_SHARD_SWIGLU = 2 };
+
+/* n_size = rows of this shard of w (interleaved gate|up rows for swiglu, a multiple of 128). */
+int krea2_gemm_i8_sharded(krea2_stream stream, int kind, size_t m, const void *a, const void *w, const float *scale,
+                          const float *a_scale, const float *gate, size_t k_size, size_t k_stride, size_t n_size,
+                          const krea2_shard *shard);
+int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch);
+
 /* bf16 <-> f16 transport of src/training/quantized.rs:63-72,102-110 (`lora_transport`,
  * reverse = 1: bf16 -> f16, reverse = 2: f16 -> bf16). */
 int krea2_lora_transport(krea2_stream stream, size_t elements, const void *src, void *dst, int reverse);

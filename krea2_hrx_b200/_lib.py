@@ -49,6 +49,11 @@ class Binding(ctypes.Structure):
     _fields_ = [("ptr", c_void_p), ("bytes", c_size_t)]
 
 
+class Shard(ctypes.Structure):
+    _fields_ = [("world", c_uint32), ("rank", c_uint32), ("dest", c_void_p * 8), ("pitch", c_size_t),
+                ("offset", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p)]
+
+
 class Dims(ctypes.Structure):
     _fields_ = [("hidden", c_size_t), ("kv_heads", c_size_t), ("head_dim", c_size_t), ("inter", c_size_t)]
 
@@ -72,6 +77,9 @@ SIGNATURES = {
     "krea2_gemm_i8_swiglu_256": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                          c_size_t, c_size_t, c_size_t]),
     "krea2_gemm_i8_acc": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
+    "krea2_gemm_i8_sharded": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                      c_size_t, c_size_t, POINTER(Shard)]),
+    "krea2_shard_wait": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32]),
     "krea2_lora_transport": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int]),
     "krea2_quantized_workspace_bytes": (c_size_t, [c_size_t, c_size_t, c_size_t]),
     "krea2_quantized_forward": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,

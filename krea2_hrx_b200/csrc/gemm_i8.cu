@@ -40,7 +40,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after t
 
 enum class Epi { Plain, Resid, Swiglu, Acc };
 
-enum StatusBits { kProducerTimedOut = 1, kMmaTimedOut = 2, kEpilogueTimedOut = 4, kDrainTimedOut = 8 };
+enum StatusBits { kProducerTimedOut = 1, kMmaTimedOut = 2, kEpilogueTimedOut = 4, kDrainTimedOut = 8, kShardWaitTimedOut = 16 };
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -228,7 +228,29 @@ struct GemmArgs {
     const float *a_scale;  // [m] per token
     const float *gate;     // [n], residual epilogue only
     void *c;               // f16 [m][n] | bf16 [m][n] in/out | f16 [m][n/2] | i32 [m][n]
+    // Column-sharded launches (template flag S): this launch owns output columns c_offset.. of rows
+    // that are c_pitch elements long, and stores every finished vector into `world` destination
+    // buffers -- its own (`c`, also the source of the residual) and the peers' copies of the same
+    // tensor, reached through peer-mapped pointers.  When the last CTA has finished, slot `rank` of
+    // every destination's flag array receives `epoch`.
+    uint32_t world, rank, c_pitch, c_offset, epoch;
+    void *dest[8];
+    uint32_t *flags[8];
+    uint32_t *done_counter;
 };
+
+// Stores one 16-byte vector at element offset `at` (16-bit elements) of the output: into `c` alone,
+// or into every destination of a sharded launch.
+template <bool S>
+__device__ __forceinline__ void store_out(const GemmArgs &g, size_t at, int v, uint4 value) {
+    if constexpr (S) {
+#pragma unroll
+        for (int d = 0; d < 8; d++)
+            if (d < static_cast<int>(g.world)) reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.dest[d]) + at)[v] = value;
+    } else {
+        reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + at)[v] = value;
+    }
+}
 
 __device__ __forceinline__ float dequant(int32_t acc, float ws, float as) {
     // kernels/gemm_i8_256.loom:610-620: sitofp, times the channel scale, times the token scale, bf16.
@@ -245,7 +267,7 @@ __device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
 }
 
 // One thread's 32 consecutive accumulator columns of one row, starting at column n.
-template <Epi E>
+template <Epi E, bool S>
 __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const GemmArgs &g, uint32_t row, uint32_t n,
                                                float as) {
     float ws[32];
@@ -254,8 +276,10 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
         for (int i = 0; i < 8; i++)
             *reinterpret_cast<float4 *>(ws + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.scale + n) + i);
     }
+    // Element offset of this chunk's first output inside a destination buffer.
+    const size_t at = S ? static_cast<size_t>(row) * g.c_pitch + g.c_offset + (E == Epi::Swiglu ? n / 2 : n)
+                        : static_cast<size_t>(row) * (E == Epi::Swiglu ? g.n / 2 : g.n) + (E == Epi::Swiglu ? n / 2 : n);
     if constexpr (E == Epi::Plain) {
-        uint4 *out = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
 #pragma unroll
         for (int v = 0; v < 4; v++) {
             uint32_t w[4];
@@ -263,11 +287,11 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
             for (int i = 0; i < 4; i++)
                 w[i] = pack_half2(dequant(acc[8 * v + 2 * i], ws[8 * v + 2 * i], as),
                                   dequant(acc[8 * v + 2 * i + 1], ws[8 * v + 2 * i + 1], as));
-            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
         }
     } else if constexpr (E == Epi::Resid) {
         // kernels/gemm_i8_resid_256.loom:622-635: bf16(lin), bf16(lin * gate), bf16(prior + gated).
-        uint4 *x = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
+        const uint4 *x = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(g.c) + at);
         float gt[32];
 #pragma unroll
         for (int i = 0; i < 8; i++)
@@ -286,13 +310,11 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
                 hi = __fadd_rn(__uint_as_float(pw[i] & 0xffff0000u), hi);
                 w[i] = pack_bf162(lo, hi);
             }
-            x[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
         }
     } else if constexpr (E == Epi::Swiglu) {
         // kernels/gemm_i8_swiglu_256.loom:612-660: columns n..n+15 are gate rows, n+16..n+31 the
         // matching up rows; 16 outputs at column n/2.
-        uint4 *out =
-            reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + static_cast<size_t>(row) * (g.n / 2) + n / 2);
 #pragma unroll
         for (int v = 0; v < 2; v++) {
             uint32_t w[4];
@@ -309,7 +331,7 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
                 }
                 w[i] = pack_half2(r[0], r[1]);
             }
-            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
         }
     } else {
         uint4 *out = reinterpret_cast<uint4 *>(static_cast<int32_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
@@ -318,7 +340,23 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
     }
 }
 
-template <Epi E, int BN>
+// After the CTA-wide (or cluster-wide) barrier that follows the last tile: the last CTA of a sharded
+// launch to get here publishes `epoch` in every destination's flag slot.  Each storing thread has
+// already fenced at system scope, so whoever observes the flag observes the stores.
+__device__ __forceinline__ void publish_shard(const GemmArgs &g) {
+    if (threadIdx.x != 0 || g.done_counter == nullptr) return;
+    __threadfence_system();
+    const uint32_t finished = atomicAdd(g.done_counter, 1u);
+    if (finished != gridDim.x - 1) return;
+    *g.done_counter = 0;  // ready for the next launch on this stream
+    __threadfence_system();
+#pragma unroll
+    for (int d = 0; d < 8; d++)
+        if (d < static_cast<int>(g.world) && g.flags[d] != nullptr)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[d] + g.rank), "r"(g.epoch) : "memory");
+}
+
+template <Epi E, int BN, bool S>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const GemmArgs g) {
@@ -450,11 +488,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c = group; c < BN / 32; c += kColumnGroups) {
                 int32_t acc[32];
                 tmem_load_32(lane_base + c * 32, acc);
-                if (in_range) epilogue_chunk<E>(acc, g, row, n0 + c * 32, as);
+                if (in_range) epilogue_chunk<E, S>(acc, g, row, n0 + c * 32, as);
             }
             tc_fence_before();
             mbar_arrive(acc_empty + a);
         }
+        if constexpr (S) __threadfence_system();
     }
 
     tc_fence_before();
@@ -464,6 +503,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         tmem_dealloc(tmem_base, T::kTmemColumns);
     }
+    if constexpr (S) publish_shard(g);
 }
 
 // ---------------------------------------------------------------- two-CTA kernel
@@ -485,7 +525,7 @@ struct PairTile {
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
-template <Epi E>
+template <Epi E, bool S>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const GemmArgs g) {
@@ -609,12 +649,13 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int c = group; c < BN / 32; c += kColumnGroups) {
                 int32_t acc[32];
                 tmem_load_32(lane_base + c * 32, acc);
-                if (in_range) epilogue_chunk<E>(acc, g, row, n0 + c * 32, as);
+                if (in_range) epilogue_chunk<E, S>(acc, g, row, n0 + c * 32, as);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty + a, 0));
         }
+        if constexpr (S) __threadfence_system();
     }
 
     tc_fence_before();
@@ -624,6 +665,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
         tmem_dealloc_pair(tmem_base, T::kTmemColumns);
     }
+    if constexpr (S) publish_shard(g);
 }
 
 // ---------------------------------------------------------------- host side
@@ -673,7 +715,7 @@ int sm_count() {
 }
 
 // Raises the kernel's dynamic shared-memory limit once per device.
-template <Epi E, int BN>
+template <Epi E, int BN, bool S = false>
 int ensure_instance() {
     static std::once_flag once[64];
     static cudaError_t attr_status[64];
@@ -681,7 +723,7 @@ int ensure_instance() {
     KREA2_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
     std::call_once(once[device], [&] {
-        attr_status[device] = cudaFuncSetAttribute(gemm_i8_kernel<E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_status[device] = cudaFuncSetAttribute(gemm_i8_kernel<E, BN, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    Tile<BN>::kSmemBytes);
     });
     if (attr_status[device] != cudaSuccess)
@@ -690,19 +732,19 @@ int ensure_instance() {
     return KREA2_OK;
 }
 
-template <Epi E, int BN>
+template <Epi E, int BN, bool S = false>
 int launch_instance(cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_w, const GemmArgs &args) {
-    if (int status = ensure_instance<E, BN>()) return status;
+    if (int status = ensure_instance<E, BN, S>()) return status;
     const uint32_t tiles = ((args.m + kBlockM - 1) / kBlockM) * (args.n / BN);
     const unsigned grid = tiles < static_cast<uint32_t>(sm_count()) ? tiles : static_cast<unsigned>(sm_count());
-    gemm_i8_kernel<E, BN><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_w, args);
+    gemm_i8_kernel<E, BN, S><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_w, args);
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 launch failed: %s", cudaGetErrorString(status));
     return KREA2_OK;
 }
 
 // Shared-memory limit and the number of two-CTA clusters this device can hold at once.
-template <Epi E>
+template <Epi E, bool S = false>
 int ensure_pair_instance(int *clusters) {
     static std::once_flag once[64];
     static cudaError_t attr_status[64];
@@ -711,7 +753,7 @@ int ensure_pair_instance(int *clusters) {
     KREA2_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
     std::call_once(once[device], [&] {
-        attr_status[device] = cudaFuncSetAttribute(gemm_i8_pair_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_status[device] = cudaFuncSetAttribute(gemm_i8_pair_kernel<E, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    PairTile::kSmemBytes);
         if (attr_status[device] != cudaSuccess) return;
         cudaLaunchConfig_t config = {};
@@ -726,7 +768,7 @@ int ensure_pair_instance(int *clusters) {
         config.attrs = &attribute;
         config.numAttrs = 1;
         int n = 0;
-        attr_status[device] = cudaOccupancyMaxActiveClusters(&n, gemm_i8_pair_kernel<E>, &config);
+        attr_status[device] = cudaOccupancyMaxActiveClusters(&n, gemm_i8_pair_kernel<E, S>, &config);
         max_clusters[device] = n;
     });
     if (attr_status[device] != cudaSuccess)
@@ -736,13 +778,13 @@ int ensure_pair_instance(int *clusters) {
     return KREA2_OK;
 }
 
-template <Epi E>
+template <Epi E, bool S = false>
 int launch_pair(cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_w, const GemmArgs &args) {
     int clusters = 0;
-    if (int status = ensure_pair_instance<E>(&clusters)) return status;
+    if (int status = ensure_pair_instance<E, S>(&clusters)) return status;
     const uint32_t tiles = ((args.m + 2 * kBlockM - 1) / (2 * kBlockM)) * (args.n / PairTile::kBN);
     const unsigned pairs = tiles < static_cast<uint32_t>(clusters) ? tiles : static_cast<unsigned>(clusters);
-    gemm_i8_pair_kernel<E><<<2 * pairs, kGemmThreads, PairTile::kSmemBytes, stream>>>(map_a, map_w, args);
+    gemm_i8_pair_kernel<E, S><<<2 * pairs, kGemmThreads, PairTile::kSmemBytes, stream>>>(map_a, map_w, args);
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 (two-CTA) launch failed: %s", cudaGetErrorString(status));
     return KREA2_OK;
@@ -772,9 +814,42 @@ int check_gemm(const char *name, size_t m, size_t k_size, size_t k_stride, size_
     return KREA2_OK;
 }
 
+// Bounded wait of one device for the flag slots its peers (and itself) publish.
+__global__ void shard_wait_kernel(const uint32_t *flags, uint32_t world, uint32_t epoch) {
+    const uint32_t r = threadIdx.x;
+    if (r >= world) return;
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+        if (static_cast<int32_t>(seen - epoch) >= 0) return;
+        if (global_timer_ns() - start > kWaitLimitNs) {
+            atomicOr(&g_device_status, kShardWaitTimedOut);
+            return;
+        }
+    }
+}
+
+int check_shard(const char *name, const krea2_shard *shard, size_t out_columns) {
+    KREA2_REQUIRE(shard->world >= 1 && shard->world <= 8 && shard->rank < shard->world,
+                  "%s: world %u / rank %u outside 1..8", name, shard->world, shard->rank);
+    KREA2_REQUIRE(shard->pitch % 16 == 0 && shard->offset % 16 == 0 && shard->offset + out_columns <= shard->pitch,
+                  "%s: columns %zu..%zu do not fit rows of %zu (both multiples of 16)", name, shard->offset,
+                  shard->offset + out_columns, shard->pitch);
+    KREA2_REQUIRE(shard->pitch <= 0xffffffffull, "%s: pitch too large", name);
+    bool any_flag = false;
+    for (uint32_t d = 0; d < shard->world; d++) {
+        KREA2_REQUIRE(shard->dest[d] && aligned16(shard->dest[d]), "%s: destination %u is null or unaligned", name, d);
+        any_flag = any_flag || shard->flags[d] != nullptr;
+    }
+    KREA2_REQUIRE(!any_flag || shard->counter, "%s: flags need the launch counter", name);
+    return KREA2_OK;
+}
+
 template <Epi E>
 int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, const void *w, const float *scale,
-             const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride, size_t n_size) {
+             const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride, size_t n_size,
+             const krea2_shard *shard = nullptr) {
     KREA2_REQUIRE(a && w && c, "%s: null buffer", name);
     KREA2_REQUIRE(aligned16(a) && aligned16(w) && aligned16(c), "%s: buffers must be 16-byte aligned", name);
     if constexpr (E != Epi::Acc) {
@@ -791,12 +866,27 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.a_scale = a_scale;
     args.gate = gate;
     args.c = c;
+    args.world = 1, args.rank = 0, args.c_pitch = 0, args.c_offset = 0, args.epoch = 0, args.done_counter = nullptr;
+    for (int d = 0; d < 8; d++) args.dest[d] = nullptr, args.flags[d] = nullptr;
+    if (shard) {
+        args.world = shard->world, args.rank = shard->rank, args.epoch = shard->epoch;
+        args.c_pitch = static_cast<uint32_t>(shard->pitch), args.c_offset = static_cast<uint32_t>(shard->offset);
+        args.done_counter = shard->counter;
+        for (uint32_t d = 0; d < shard->world; d++) args.dest[d] = shard->dest[d], args.flags[d] = shard->flags[d];
+    }
     const bool wide = n_size % 256 == 0;
     // The two-CTA kernel wants whole 256-column tiles and more than one 128-row half to fill.
     const bool pair = wide && m > kBlockM && pair_enabled();
     CUtensorMap map_a, map_w;
     if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
     if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, (wide && !pair) ? 256 : 128)) return status;
+    if constexpr (E != Epi::Acc) {
+        if (shard) {
+            if (pair) return launch_pair<E, true>(stream, map_a, map_w, args);
+            return wide ? launch_instance<E, 256, true>(stream, map_a, map_w, args)
+                        : launch_instance<E, 128, true>(stream, map_a, map_w, args);
+        }
+    }
     if (pair) return launch_pair<E>(stream, map_a, map_w, args);
     return wide ? launch_instance<E, 256>(stream, map_a, map_w, args)
                 : launch_instance<E, 128>(stream, map_a, map_w, args);
@@ -874,6 +964,35 @@ extern "C" int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, c
     if (int status = check_gemm("gemm_i8_acc", m, k_size, k_stride, n_size, 1, 64, 128)) return status;
     return run_gemm<Epi::Acc>("gemm_i8_acc", static_cast<cudaStream_t>(stream), m, a, w, nullptr, nullptr, acc,
                               nullptr, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_sharded(krea2_stream stream, int kind, size_t m, const void *a, const void *w,
+                                     const float *scale, const float *a_scale, const float *gate, size_t k_size,
+                                     size_t k_stride, size_t n_size, const krea2_shard *shard) {
+    clear_error();
+    KREA2_REQUIRE(shard, "gemm_i8_sharded: shard description is null");
+    KREA2_REQUIRE(kind >= KREA2_SHARD_PLAIN && kind <= KREA2_SHARD_SWIGLU, "gemm_i8_sharded: unknown kind %d", kind);
+    if (int status = check_gemm("gemm_i8_sharded", m, k_size, k_stride, n_size, 1, 128, 128)) return status;
+    const size_t out_columns = kind == KREA2_SHARD_SWIGLU ? n_size / 2 : n_size;
+    if (int status = check_shard("gemm_i8_sharded", shard, out_columns)) return status;
+    void *own = shard->dest[shard->rank];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kind == KREA2_SHARD_PLAIN)
+        return run_gemm<Epi::Plain>("gemm_i8_sharded", st, m, a, w, scale, a_scale, own, nullptr, k_size, k_stride, n_size,
+                                    shard);
+    if (kind == KREA2_SHARD_SWIGLU)
+        return run_gemm<Epi::Swiglu>("gemm_i8_sharded", st, m, a, w, scale, a_scale, own, nullptr, k_size, k_stride, n_size,
+                                     shard);
+    return run_gemm<Epi::Resid>("gemm_i8_sharded", st, m, a, w, scale, a_scale, own, gate, k_size, k_stride, n_size, shard);
+}
+
+extern "C" int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch) {
+    clear_error();
+    KREA2_REQUIRE(flags && world >= 1 && world <= 8, "shard_wait: flags null or world outside 1..8");
+    shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(KREA2_RUNTIME, "shard_wait launch failed: %s", cudaGetErrorString(status));
+    return KREA2_OK;
 }
 
 extern "C" int krea2_device_status(int *host_status) {

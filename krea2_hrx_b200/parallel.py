@@ -1,0 +1,275 @@
+"""Running the block chain on several GPUs.
+
+Two ways the W8A8 path spreads over devices, neither of which exists in the reference (one APU):
+
+* data parallel over images -- one ordinary `session.Session` per device, no communication
+  (`bench.py --gpus N`); nothing here is needed for it;
+* column-sharded weights within one image (`TensorParallel`, below): device r holds rows
+  [r*N/g, (r+1)*N/g) of every weight, runs the prologues redundantly (they are cheap), computes its
+  column slab of each GEMM and lets the epilogue store every finished vector into all devices'
+  copies of the output through peer-mapped pointers (`krea2_gemm_i8_sharded`).  A flag per device
+  and launch, waited on by `krea2_shard_wait`, tells each device when every slab has landed.  No
+  arithmetic changes, so the result is bit-identical to the single-device session.
+  `TensorParallel.forward(..., collective="nccl")` is the baseline the fused path is compared with:
+  the same sharded GEMMs into local buffers, then an NCCL all-gather and a local repack.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import shape
+from ._lib import InvalidArgument, Shard, check, lib
+from .session import ModelDims, Weights
+
+PLAIN, RESID, SWIGLU = 0, 1, 2
+
+
+def shard_columns(n: int, world: int, multiple: int) -> List[Tuple[int, int]]:
+    """(first row, rows) of each device's share of a weight with `n` rows; every share is the same
+    whole number of `multiple`-row units (128 for the GEMM tile; 32 interleaved rows = 16 outputs
+    keep a gate|up pair together, and 128 covers that too)."""
+    if world < 1 or world > 8:
+        raise InvalidArgument("world must be 1..8")
+    if n % (world * multiple) != 0:
+        raise InvalidArgument(f"{n} rows do not split into {world} shares of whole {multiple}-row units")
+    size = n // world
+    return [(r * size, size) for r in range(world)]
+
+
+def column_slab(full: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """Rank's contiguous copy of its column slab of a row-major [rows][width] tensor."""
+    size = full.shape[1] // world
+    return full[:, rank * size:(rank + 1) * size].contiguous()
+
+
+def assemble_columns(full: torch.Tensor, gathered: torch.Tensor) -> None:
+    """Writes all-gathered slabs [world][rows][width/world] back as the columns of `full`."""
+    world, rows, size = gathered.shape
+    full.view(rows, world, size).copy_(gathered.permute(1, 0, 2))
+
+
+class DeviceView:
+    """A raw device pointer as something torch can wrap (for slicing spans of `Weights`)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def span_tensor(weights: Weights, name: str, dtype: torch.dtype) -> torch.Tensor:
+    ptr, nbytes = weights.locate(name)
+    return torch.as_tensor(DeviceView(ptr, nbytes), device="cuda").view(dtype)
+
+
+@dataclass
+class BlockShard:
+    """One device's share of a block's weights (rows of each operand and the matching scales)."""
+    qkvg_q: torch.Tensor
+    qkvg_s: torch.Tensor
+    wo_q: torch.Tensor
+    wo_s: torch.Tensor
+    gu_q: torch.Tensor
+    gu_s: torch.Tensor
+    down_q: torch.Tensor
+    down_s: torch.Tensor
+    prenorm: torch.Tensor
+    postnorm: torch.Tensor
+
+
+def shard_weights(weights: Weights, layers: int, world: int, rank: int) -> List[BlockShard]:
+    """Slices every operand of `weights` (the full plan layout) into rank's rows."""
+    d = weights.dims
+    ph, pi = shape.gemm_pitch(d.hidden), shape.gemm_pitch(d.inter)
+    out = []
+    for i in range(layers):
+        p = f"blocks.{i}"
+
+        def rows(name, n, pitch):
+            first, count = shard_columns(n, world, 128)[rank]
+            q = span_tensor(weights, f"{p}.{name}.q", torch.int8).view(n, pitch)[first:first + count].clone()
+            s = span_tensor(weights, f"{p}.{name}.s", torch.float32)[first:first + count].clone()
+            return q, s
+
+        qkvg = rows("qkvg", d.qkvg, ph)
+        wo = rows("wo", d.hidden, ph)
+        gu = rows("gu", 2 * d.inter, ph)
+        down = rows("down", d.hidden, pi)
+        out.append(BlockShard(*qkvg, *wo, *gu, *down,
+                              span_tensor(weights, f"{p}.prenorm", torch.float32).clone(),
+                              span_tensor(weights, f"{p}.postnorm", torch.float32).clone()))
+    return out
+
+
+class LocalFabric:
+    """All "devices" are buffers on the current GPU: the single-GPU stand-in used to test the
+    sharded path (every rank's launches go to one stream, in stage order)."""
+
+    def __init__(self, world: int):
+        self.world = world
+        self._buffers = {}
+
+    def allocate(self, name: str, rank: int, shape_, dtype) -> torch.Tensor:
+        t = torch.zeros(shape_, dtype=dtype, device="cuda")
+        self._buffers.setdefault(name, {})[rank] = t
+        return t
+
+    def pointers(self, name: str, rank: int) -> List[int]:
+        return [self._buffers[name][r].data_ptr() for r in range(self.world)]
+
+    def barrier(self) -> None:
+        torch.cuda.synchronize()
+
+
+class SymmetricFabric:
+    """One process per GPU: buffers come from torch's symmetric memory, whose rendezvous hands every
+    rank the peer-mapped address of every other rank's buffer."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self._dist, self._symm = dist, symm
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self._handles = {}
+
+    def allocate(self, name: str, rank: int, shape_, dtype) -> torch.Tensor:
+        t = self._symm.empty(shape_, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        handle = self._symm.rendezvous(t, self.group)
+        t.zero_()
+        self._handles[name] = (t, handle)
+        return t
+
+    def pointers(self, name: str, rank: int) -> List[int]:
+        return [int(p) for p in self._handles[name][1].buffer_ptrs]
+
+    def barrier(self) -> None:
+        torch.cuda.synchronize()
+        self._dist.barrier(self.group)
+        torch.cuda.synchronize()
+
+
+class TensorParallel:
+    """One device's part of a column-sharded run of `layers` blocks over `tokens` rows."""
+
+    def __init__(self, fabric, rank: int, dims: ModelDims, shards: Sequence[BlockShard], tokens: int,
+                 stream: Optional[torch.cuda.Stream] = None):
+        self.fabric, self.rank, self.world = fabric, rank, fabric.world
+        self.dims, self.shards, self.tokens = dims, list(shards), tokens
+        self.stream = stream or torch.cuda.current_stream()
+        cap = shape.capacity(tokens)
+        d = dims
+        self.ph, self.pi = shape.gemm_pitch(d.hidden), shape.gemm_pitch(d.inter)
+        wide = max(d.hidden, d.inter)
+        self.x = fabric.allocate("x", rank, (cap, d.hidden), torch.bfloat16)
+        self.fused = fabric.allocate("fused", rank, (cap, d.qkvg), torch.float16)
+        self.attn_gu = fabric.allocate("attn_gu", rank, (cap, wide), torch.float16)
+        self.flags = fabric.allocate("flags", rank, (8,), torch.int32)
+        self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.a_q = torch.zeros((cap, shape.gemm_pitch(wide)), dtype=torch.int8, device="cuda")
+        self.a_s = torch.zeros(cap, dtype=torch.float32, device="cuda")
+        self.epoch = 0
+        self.launches = 0
+
+    # -- launches ---------------------------------------------------------------------------
+    def _sharded(self, kind, w, s, gate, k, pitch, n_total, out_name, out_pitch, collective) -> None:
+        first, count = shard_columns(n_total, self.world, 128)[self.rank]
+        out_first = first // 2 if kind == SWIGLU else first
+        desc = Shard()
+        if collective == "fused":
+            desc.world, desc.rank = self.world, self.rank
+            for r, ptr in enumerate(self.fabric.pointers(out_name, self.rank)):
+                desc.dest[r] = ptr
+            for r, ptr in enumerate(self.fabric.pointers("flags", self.rank)):
+                desc.flags[r] = ptr
+            self.epoch += 1
+            desc.epoch = self.epoch
+            desc.counter = self.counter.data_ptr()
+        else:  # the slab goes to the local copy only; a collective moves it afterwards
+            desc.world, desc.rank = 1, 0
+            desc.dest[0] = getattr(self, out_name).data_ptr()
+        desc.pitch, desc.offset = out_pitch, out_first
+        # the residual gate is indexed by output column: this shard's slice of it
+        gate_ptr = gate[first:first + count].data_ptr() if gate is not None else None
+        check(lib().krea2_gemm_i8_sharded(self.stream.cuda_stream, kind, self.tokens, self.a_q.data_ptr(), w.data_ptr(),
+                                          s.data_ptr(), self.a_s.data_ptr(), gate_ptr, k, pitch, count,
+                                          ctypes.byref(desc)))
+        self.launches += 1
+
+    def _wait(self) -> None:
+        check(lib().krea2_shard_wait(self.stream.cuda_stream, self.flags.data_ptr(), self.world, self.epoch))
+
+    def _gather(self, out_name: str, n_total: int, swiglu: bool) -> None:
+        """The NCCL baseline: all-gather of the column slabs, then a repack into row-major."""
+        import torch.distributed as dist
+        width = n_total // 2 if swiglu else n_total
+        t = self.tokens
+        full = getattr(self, out_name).view(-1)[: t * width].view(t, width)
+        gathered = torch.empty((self.world, t, width // self.world), dtype=full.dtype, device=full.device)
+        dist.all_gather_into_tensor(gathered, column_slab(full, self.world, self.rank), group=self.fabric.group)
+        assemble_columns(full, gathered)
+
+    # -- the chain --------------------------------------------------------------------------
+    def stages(self, mods: torch.Tensor, collective: str = "fused") -> Iterator[None]:
+        """The block chain as a sequence of steps; every `yield` is a point where, on a single GPU
+        standing in for several, the other ranks' launches of the same step must be issued before
+        this rank goes on (in one process per GPU the generator is simply run to its end)."""
+        from . import ops
+        d, t, st = self.dims, self.tokens, self.stream
+        h, inter, qkvg = d.hidden, d.inter, d.qkvg
+
+        def after_gemm(name, n_total, swiglu=False):
+            if collective == "fused":
+                self._wait()
+            elif self.world > 1:
+                self._gather(name, n_total, swiglu)
+
+        for i, w in enumerate(self.shards):
+            m = mods[i]
+            ops.prepare_norm_i8(self.x[:t], w.prenorm, m[0], m[1], self.a_q, self.a_s, h, self.ph, 1e-5, st)
+            self._sharded(PLAIN, w.qkvg_q, w.qkvg_s, None, h, self.ph, qkvg, "fused", qkvg, collective)
+            yield
+            after_gemm("fused", qkvg)
+            self.attn_gu[:t].view(-1)[: t * h].view(t, h).copy_(self.fused[:t, :h])  # attention stand-in
+            attn = self.attn_gu.view(-1)[: t * h].view(t, h)
+            ops.prepare_gated_i8(attn, self.fused.view(-1)[d.gate_offset:], self.a_q, self.a_s, h, self.ph, qkvg, st,
+                                 tokens=t)
+            self._sharded(RESID, w.wo_q, w.wo_s, m[2], h, self.ph, h, "x", h, collective)
+            yield
+            after_gemm("x", h)
+            ops.prepare_norm_i8(self.x[:t], w.postnorm, m[3], m[4], self.a_q, self.a_s, h, self.ph, 1e-5, st)
+            self._sharded(SWIGLU, w.gu_q, w.gu_s, None, h, self.ph, 2 * inter, "attn_gu", inter, collective)
+            yield
+            after_gemm("attn_gu", 2 * inter, swiglu=True)
+            gu = self.attn_gu.view(-1)[: t * inter].view(t, inter)
+            ops.prepare_plain_i8(gu, self.a_q, self.a_s, inter, self.pi, st)
+            self._sharded(RESID, w.down_q, w.down_s, m[5], inter, self.pi, h, "x", h, collective)
+            yield
+            after_gemm("x", h)
+
+    def forward(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused") -> torch.Tensor:
+        """x: device bf16 [tokens][hidden] (the same on every rank); returns the new residual stream."""
+        self.x[: self.tokens].copy_(x)
+        for _ in self.stages(mods, collective):
+            pass
+        return self.x[: self.tokens]
+
+
+def run_emulated(ranks: Sequence[TensorParallel], x: torch.Tensor, mods: torch.Tensor) -> List[torch.Tensor]:
+    """Drives every rank of a `LocalFabric` on one GPU, step by step, so that each step's launches
+    of all ranks are queued before anything waits for them."""
+    for r in ranks:
+        r.x[: r.tokens].copy_(x)
+    generators = [r.stages(mods, "fused") for r in ranks]
+    while True:
+        finished = 0
+        for g in generators:
+            try:
+                next(g)
+            except StopIteration:
+                finished += 1
+        if finished == len(generators):
+            break
+    return [r.x[: r.tokens] for r in ranks]

@@ -1,0 +1,93 @@
+"""The column-sharded chain.  On one GPU every rank's buffers live on the same device and the
+ranks' launches are interleaved step by step (parallel.run_emulated); on two or more GPUs a
+torchrun child process per GPU runs the fused push and the NCCL baseline (tests/tp_worker.py).
+Either way the residual stream must equal the single-device session's bit for bit."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import session_oracle as so
+
+pytestmark = pytest.mark.gpu
+
+k = pytest.importorskip("krea2_hrx_b200")
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_sharded_chain_on_one_gpu_equals_the_session(world):
+    from krea2_hrx_b200 import parallel, session
+    dims = session.ModelDims(**so.SMALL)
+    layers, tokens = 2, 300
+    stream = torch.cuda.current_stream()
+    weights = session.Weights(dims, layers)
+    weights.fill_synthetic(11, stream)
+    x, mods, cos, sin = so.make_inputs(dims, tokens, layers, seed=world)
+    single = session.Session(stream, weights, tokens, layers)
+    want = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    single.run(stream, want, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    fabric = parallel.LocalFabric(world)
+    ranks = [parallel.TensorParallel(fabric, r, dims, parallel.shard_weights(weights, layers, world, r), tokens)
+             for r in range(world)]
+    x_dev = torch.from_numpy(x.copy()).view(torch.bfloat16).cuda()
+    mods_dev = torch.from_numpy(mods).cuda()
+    for _ in range(2):  # twice: flags and epochs carry over between forwards
+        outs = parallel.run_emulated(ranks, x_dev, mods_dev)
+        torch.cuda.synchronize()
+        for out in outs:
+            np.testing.assert_array_equal(bits(out), bits(want))
+    assert ranks[0].launches == 2 * layers * 4
+    assert k.device_status() == 0
+    single.close()
+
+
+def test_sharded_gemm_refuses_bad_descriptions():
+    from krea2_hrx_b200 import _lib
+    import ctypes
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = buf.data_ptr()
+    desc = _lib.Shard()
+    desc.world, desc.rank, desc.pitch, desc.offset = 2, 0, 256, 128
+    desc.dest[0] = p
+    desc.dest[1] = p
+
+    def call(kind=0, n=128):
+        return k.lib().krea2_gemm_i8_sharded(None, kind, 16, p, p, p, p, p, 128, 128, n, ctypes.byref(desc)), \
+            k.lib().krea2_last_error().decode()
+    status, message = call(n=256)
+    assert status == 1 and "do not fit" in message
+    desc.offset = 8
+    status, message = call()
+    assert status == 1 and "multiples of 16" in message
+    desc.offset, desc.world = 0, 9
+    status, message = call()
+    assert status == 1 and "world" in message
+    desc.world = 2
+    desc.dest[1] = None
+    status, message = call()
+    assert status == 1 and "destination 1" in message
+    status, message = call(kind=7)
+    assert status == 1 and "unknown kind" in message
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_chain_on_two_gpus_fused_and_nccl():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    worker = os.path.join(os.path.dirname(__file__), "tp_worker.py")
+    world = min(torch.cuda.device_count(), 4)
+    world = 2 if world < 4 else 4
+    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                             "--master-addr", "127.0.0.1", "--master-port", str(port), worker, "--check"],
+                            capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    assert "tp check ok" in result.stdout

@@ -1,0 +1,65 @@
+"""Host logic of the multi-GPU paths on CPU: shard boundaries, and (two gloo ranks) that
+all-gathered column slabs reassemble the row-major tensor the single-device path produces."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import krea2_hrx_b200 as k
+from krea2_hrx_b200 import parallel
+
+
+def test_shard_columns_split_whole_tiles():
+    assert parallel.shard_columns(15360, 2, 128) == [(0, 7680), (7680, 7680)]
+    assert parallel.shard_columns(15360, 8, 128)[7] == (13440, 1920)
+    assert parallel.shard_columns(32768, 8, 128)[3] == (12288, 4096)
+    assert parallel.shard_columns(6144, 1, 128) == [(0, 6144)]
+    with pytest.raises(k.InvalidArgument, match="do not split"):
+        parallel.shard_columns(6144 + 128, 8, 128)
+    with pytest.raises(k.InvalidArgument, match="world must be"):
+        parallel.shard_columns(6144, 9, 128)
+    # every share keeps gate|up pairs together: 32 interleaved rows = 16 outputs
+    for first, count in parallel.shard_columns(32768, 8, 128):
+        assert first % 32 == 0 and count % 32 == 0
+
+
+def _gather_worker(rank, world, port, failures):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(5)
+        rows, width = 37, 512
+        want = torch.randn((rows, width), generator=gen)  # the same on every rank
+        mine = torch.zeros_like(want)
+        size = width // world
+        mine[:, rank * size:(rank + 1) * size] = want[:, rank * size:(rank + 1) * size]  # this rank's slab only
+        gathered = [torch.empty((rows, size)) for _ in range(world)]
+        dist.all_gather(gathered, parallel.column_slab(mine, world, rank))
+        parallel.assemble_columns(mine, torch.stack(gathered))
+        if not torch.equal(mine, want):
+            failures.put(f"rank {rank}: reassembled tensor differs")
+        # data-parallel timing rule: the slowest rank defines the step
+        t = torch.tensor([10.0 + rank], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if t.item() != 10.0 + world - 1:
+            failures.put(f"rank {rank}: max-over-ranks gave {t.item()}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reassemble_column_slabs():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert failures.empty(), failures.get()
