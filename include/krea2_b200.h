@@ -110,7 +110,7 @@ int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *
  * over NVLink instead of following as a separate collective.  Each output element is still one
  * full-K dot product of one CTA, so sharded results are bit-identical to the single-device ones.
  * When the last CTA of a launch has finished, slot `rank` of every destination's flag array is
- * set to `epoch`; krea2_shard_wait makes a stream wait (bounded, 2 s, then the device status
+ * set to `epoch` (+ *epoch_base); krea2_shard_wait makes a stream wait (bounded, 2 s, then the device status
  * word is raised) until all `world` slots of the local array have reached `epoch`. */
 typedef struct krea2_shard {
     uint32_t world;     /* destination buffers, 1..8 */
@@ -122,6 +122,9 @@ typedef struct krea2_shard {
     uint32_t *flags[8]; /* per destination, `world` u32 slots; NULL entries are not signalled */
     uint32_t epoch;     /* value published when this launch's stores are complete */
     uint32_t *counter;  /* u32 on this device, zero before the first launch (the kernel re-zeroes it) */
+    const uint32_t *epoch_base; /* optional device word added to `epoch` when publishing: a chain captured
+                                   in a CUDA graph keeps its epochs relative and advances this word (with
+                                   krea2_shard_advance) at the end of every replay */
 } krea2_shard;
 
 enum { KREA2_SHARD_PLAIN = 0, KREA2_SHARD_RESID = 1, KREA2_SHARD_SWIGLU = 2 };
@@ -130,7 +133,9 @@ enum { KREA2_SHARD_PLAIN = 0, KREA2_SHARD_RESID = 1, KREA2_SHARD_SWIGLU = 2 };
 int krea2_gemm_i8_sharded(krea2_stream stream, int kind, size_t m, const void *a, const void *w, const float *scale,
                           const float *a_scale, const float *gate, size_t k_size, size_t k_stride, size_t n_size,
                           const krea2_shard *shard);
-int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch);
+int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch,
+                     const uint32_t *epoch_base);
+int krea2_shard_advance(krea2_stream stream, uint32_t *epoch_base, uint32_t delta);
 
 /* bf16 <-> f16 transport of src/training/quantized.rs:63-72,102-110 (`lora_transport`,
  * reverse = 1: bf16 -> f16, reverse = 2: f16 -> bf16). */

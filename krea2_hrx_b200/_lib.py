@@ -51,7 +51,7 @@ class Binding(ctypes.Structure):
 
 class Shard(ctypes.Structure):
     _fields_ = [("world", c_uint32), ("rank", c_uint32), ("dest", c_void_p * 8), ("pitch", c_size_t),
-                ("offset", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p)]
+                ("offset", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p), ("epoch_base", c_void_p)]
 
 
 class Dims(ctypes.Structure):
@@ -79,7 +79,8 @@ SIGNATURES = {
     "krea2_gemm_i8_acc": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
     "krea2_gemm_i8_sharded": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                       c_size_t, c_size_t, POINTER(Shard)]),
-    "krea2_shard_wait": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32]),
+    "krea2_shard_wait": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "krea2_shard_advance": (c_int, [c_void_p, c_void_p, c_uint32]),
     "krea2_lora_transport": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int]),
     "krea2_quantized_workspace_bytes": (c_size_t, [c_size_t, c_size_t, c_size_t]),
     "krea2_quantized_forward": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,

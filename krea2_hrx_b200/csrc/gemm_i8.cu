@@ -36,6 +36,7 @@ constexpr int kEpilogueWarps = 8;   // two warps per 32-lane quarter of tensor m
 constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kGemmThreads = (kEpilogueWarps + 2) * 32;
+constexpr int kStagingBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output on their way out
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after two seconds
 
 enum class Epi { Plain, Resid, Swiglu, Acc };
@@ -219,7 +220,7 @@ struct Tile {
     static constexpr int kTmemColumns = 2 * BN;
     // stages, then barriers (full, empty per stage; full, empty per accumulator), the TMEM
     // base and the abort flag; 1024 spare bytes to align the stages.
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpilogueWarps * kStagingBytes;
 };
 
 struct GemmArgs {
@@ -237,18 +238,19 @@ struct GemmArgs {
     void *dest[8];
     uint32_t *flags[8];
     uint32_t *done_counter;
+    const uint32_t *epoch_base;  // optional device word added to `epoch` (lets a replayed graph count on)
 };
 
-// Stores one 16-byte vector at element offset `at` (16-bit elements) of the output: into `c` alone,
-// or into every destination of a sharded launch.
+// Stores one 16-byte vector at byte offset `at` of the output: into `c` alone, or into every
+// destination of a sharded launch.
 template <bool S>
-__device__ __forceinline__ void store_out(const GemmArgs &g, size_t at, int v, uint4 value) {
+__device__ __forceinline__ void store_out(const GemmArgs &g, size_t at, uint4 value) {
     if constexpr (S) {
 #pragma unroll
         for (int d = 0; d < 8; d++)
-            if (d < static_cast<int>(g.world)) reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.dest[d]) + at)[v] = value;
+            if (d < static_cast<int>(g.world)) *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(g.dest[d]) + at) = value;
     } else {
-        reinterpret_cast<uint4 *>(static_cast<uint16_t *>(g.c) + at)[v] = value;
+        *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(g.c) + at) = value;
     }
 }
 
@@ -266,19 +268,24 @@ __device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&b);
 }
 
-// One thread's 32 consecutive accumulator columns of one row, starting at column n.
-template <Epi E, bool S>
-__device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const GemmArgs &g, uint32_t row, uint32_t n,
-                                               float as) {
+// Output of one thread's 32 accumulator columns: 16-byte vectors per chunk and bytes per element.
+template <Epi E>
+struct Out {
+    static constexpr int kVectors = E == Epi::Acc ? 8 : (E == Epi::Swiglu ? 2 : 4);
+    static constexpr int kElementBytes = E == Epi::Acc ? 4 : 2;
+};
+
+// One thread's 32 consecutive accumulator columns of one row, starting at (shard-local) column n,
+// turned into that row's output vectors.  `prior` points at the same columns of the residual row.
+template <Epi E>
+__device__ __forceinline__ void epilogue_math(const int32_t (&acc)[32], const GemmArgs &g, uint32_t n, float as,
+                                              const uint4 *prior, uint4 (&out)[Out<E>::kVectors]) {
     float ws[32];
     if constexpr (E != Epi::Acc) {
 #pragma unroll
         for (int i = 0; i < 8; i++)
             *reinterpret_cast<float4 *>(ws + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.scale + n) + i);
     }
-    // Element offset of this chunk's first output inside a destination buffer.
-    const size_t at = S ? static_cast<size_t>(row) * g.c_pitch + g.c_offset + (E == Epi::Swiglu ? n / 2 : n)
-                        : static_cast<size_t>(row) * (E == Epi::Swiglu ? g.n / 2 : g.n) + (E == Epi::Swiglu ? n / 2 : n);
     if constexpr (E == Epi::Plain) {
 #pragma unroll
         for (int v = 0; v < 4; v++) {
@@ -287,19 +294,18 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
             for (int i = 0; i < 4; i++)
                 w[i] = pack_half2(dequant(acc[8 * v + 2 * i], ws[8 * v + 2 * i], as),
                                   dequant(acc[8 * v + 2 * i + 1], ws[8 * v + 2 * i + 1], as));
-            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
+            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     } else if constexpr (E == Epi::Resid) {
         // kernels/gemm_i8_resid_256.loom:622-635: bf16(lin), bf16(lin * gate), bf16(prior + gated).
-        const uint4 *x = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(g.c) + at);
         float gt[32];
 #pragma unroll
         for (int i = 0; i < 8; i++)
             *reinterpret_cast<float4 *>(gt + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.gate + n) + i);
 #pragma unroll
         for (int v = 0; v < 4; v++) {
-            uint4 prior = x[v];
-            const uint32_t pw[4] = {prior.x, prior.y, prior.z, prior.w};
+            const uint4 before = prior[v];
+            const uint32_t pw[4] = {before.x, before.y, before.z, before.w};
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -310,7 +316,7 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
                 hi = __fadd_rn(__uint_as_float(pw[i] & 0xffff0000u), hi);
                 w[i] = pack_bf162(lo, hi);
             }
-            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
+            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     } else if constexpr (E == Epi::Swiglu) {
         // kernels/gemm_i8_swiglu_256.loom:612-660: columns n..n+15 are gate rows, n+16..n+31 the
@@ -331,12 +337,68 @@ __device__ __forceinline__ void epilogue_chunk(const int32_t (&acc)[32], const G
                 }
                 w[i] = pack_half2(r[0], r[1]);
             }
-            store_out<S>(g, at, v, make_uint4(w[0], w[1], w[2], w[3]));
+            out[v] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     } else {
-        uint4 *out = reinterpret_cast<uint4 *>(static_cast<int32_t *>(g.c) + static_cast<size_t>(row) * g.n + n);
 #pragma unroll
         for (int v = 0; v < 8; v++) out[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+    }
+}
+
+// One epilogue warp's share of a finished accumulator tile: 32 rows (its TMEM lane quarter) by
+// kChunks consecutive 32-column chunks starting at chunk `first_chunk`.  Every thread computes the
+// output vectors of its own row; they go through a 4 KB per-warp staging area in shared memory
+// (16-byte pieces xor-swizzled by row, so both the row-wise writes and the piece-wise reads are
+// conflict-free) and leave as stores in which P lanes cover P*16 contiguous bytes of one row:
+// 128-byte row segments instead of 16-byte pieces scattered over 32 rows, which is what the
+// memory system -- and a peer GPU's NVLink port in a sharded launch -- wants.
+template <Epi E, bool S, int kChunks>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs &g, uint32_t tmem_lane_base, uint32_t row_base,
+                                              uint32_t n0, int first_chunk, uint8_t *stage, int lane) {
+    constexpr int NV = Out<E>::kVectors;
+    constexpr int EB = Out<E>::kElementBytes;
+    constexpr int P = (kChunks * NV) < 8 ? (kChunks * NV) : 8;  // pieces of 16 bytes per row and flush
+    static_assert(P == 4 || P == 8, "a flush covers 64 or 128 bytes of a row");
+    constexpr int kRowsPerStore = 32 / P;
+    const uint32_t row = row_base + lane;
+    const bool in_range = row < g.m;
+    // Output geometry in elements: row pitch, and the column of this launch's first output.
+    const size_t pitch = S ? g.c_pitch : (E == Epi::Swiglu ? g.n / 2 : g.n);
+    const size_t column0 = (S ? g.c_offset : 0);
+    float as = 0.0f;
+    if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
+    int slot = 0;
+    uint32_t flush_n = n0 + first_chunk * 32;  // accumulator column of the first piece awaiting a flush
+#pragma unroll 1
+    for (int cc = 0; cc < kChunks; cc++) {
+        const uint32_t n = n0 + (first_chunk + cc) * 32;
+        int32_t acc[32];
+        tmem_load_32(tmem_lane_base + (first_chunk + cc) * 32, acc);
+        uint4 out[NV];
+        if (in_range) {
+            const uint4 *prior = nullptr;
+            if constexpr (E == Epi::Resid)
+                prior = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(g.c) + row * pitch + column0 + n);
+            epilogue_math<E>(acc, g, n, as, prior, out);
+        }
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+            *reinterpret_cast<uint4 *>(stage + lane * (P * 16) + (((slot + v) ^ (lane & (P - 1))) * 16)) = out[v];
+        slot += NV;
+        if (slot == P) {
+            __syncwarp();
+            const size_t out_column = column0 + (E == Epi::Swiglu ? flush_n / 2 : flush_n);
+#pragma unroll
+            for (int j = 0; j < P; j++) {
+                const int r = j * kRowsPerStore + lane / P, piece = lane % P;
+                const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * (P * 16) + ((piece ^ (r & (P - 1))) * 16));
+                const uint32_t out_row = row_base + r;
+                if (out_row < g.m) store_out<S>(g, (out_row * pitch + out_column) * EB + piece * 16, value);
+            }
+            __syncwarp();
+            slot = 0;
+            flush_n = n + 32;
+        }
     }
 }
 
@@ -349,11 +411,12 @@ __device__ __forceinline__ void publish_shard(const GemmArgs &g) {
     const uint32_t finished = atomicAdd(g.done_counter, 1u);
     if (finished != gridDim.x - 1) return;
     *g.done_counter = 0;  // ready for the next launch on this stream
+    const uint32_t value = g.epoch + (g.epoch_base ? *g.epoch_base : 0u);
     __threadfence_system();
 #pragma unroll
     for (int d = 0; d < 8; d++)
         if (d < static_cast<int>(g.world) && g.flags[d] != nullptr)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[d] + g.rank), "r"(g.epoch) : "memory");
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[d] + g.rank), "r"(value) : "memory");
 }
 
 template <Epi E, int BN, bool S>
@@ -369,6 +432,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint8_t *staging = smem + T::kStages * T::kStageBytes + 256;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
@@ -479,17 +543,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
-            const uint32_t row = m0 + quarter * 32 + lane;
-            const bool in_range = row < g.m;
-            float as = 0.0f;
-            if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
             const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c = group; c < BN / 32; c += kColumnGroups) {
-                int32_t acc[32];
-                tmem_load_32(lane_base + c * 32, acc);
-                if (in_range) epilogue_chunk<E, S>(acc, g, row, n0 + c * 32, as);
-            }
+            constexpr int kChunks = BN / 32 / kColumnGroups;
+            epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
+                                         lane);
             tc_fence_before();
             mbar_arrive(acc_empty + a);
         }
@@ -522,7 +579,7 @@ struct PairTile {
     static constexpr int kBBytes = (kBN / 2) * kBlockK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemColumns = 2 * kBN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpilogueWarps * kStagingBytes;
 };
 
 template <Epi E, bool S>
@@ -539,6 +596,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint8_t *staging = smem + T::kStages * T::kStageBytes + 256;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -640,17 +698,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
-            const uint32_t row = m0 + quarter * 32 + lane;
-            const bool in_range = row < g.m;
-            float as = 0.0f;
-            if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
             const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c = group; c < BN / 32; c += kColumnGroups) {
-                int32_t acc[32];
-                tmem_load_32(lane_base + c * 32, acc);
-                if (in_range) epilogue_chunk<E, S>(acc, g, row, n0 + c * 32, as);
-            }
+            constexpr int kChunks = BN / 32 / kColumnGroups;
+            epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
+                                         lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty + a, 0));
@@ -815,9 +866,12 @@ int check_gemm(const char *name, size_t m, size_t k_size, size_t k_stride, size_
 }
 
 // Bounded wait of one device for the flag slots its peers (and itself) publish.
-__global__ void shard_wait_kernel(const uint32_t *flags, uint32_t world, uint32_t epoch) {
+__global__ void shard_advance_kernel(uint32_t *epoch_base, uint32_t delta) { *epoch_base += delta; }
+
+__global__ void shard_wait_kernel(const uint32_t *flags, uint32_t world, uint32_t epoch, const uint32_t *epoch_base) {
     const uint32_t r = threadIdx.x;
     if (r >= world) return;
+    if (epoch_base) epoch += *epoch_base;
     const uint64_t start = global_timer_ns();
     for (;;) {
         uint32_t seen;
@@ -867,11 +921,13 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.gate = gate;
     args.c = c;
     args.world = 1, args.rank = 0, args.c_pitch = 0, args.c_offset = 0, args.epoch = 0, args.done_counter = nullptr;
+    args.epoch_base = nullptr;
     for (int d = 0; d < 8; d++) args.dest[d] = nullptr, args.flags[d] = nullptr;
     if (shard) {
         args.world = shard->world, args.rank = shard->rank, args.epoch = shard->epoch;
         args.c_pitch = static_cast<uint32_t>(shard->pitch), args.c_offset = static_cast<uint32_t>(shard->offset);
         args.done_counter = shard->counter;
+        args.epoch_base = shard->epoch_base;
         for (uint32_t d = 0; d < shard->world; d++) args.dest[d] = shard->dest[d], args.flags[d] = shard->flags[d];
     }
     const bool wide = n_size % 256 == 0;
@@ -986,10 +1042,20 @@ extern "C" int krea2_gemm_i8_sharded(krea2_stream stream, int kind, size_t m, co
     return run_gemm<Epi::Resid>("gemm_i8_sharded", st, m, a, w, scale, a_scale, own, gate, k_size, k_stride, n_size, shard);
 }
 
-extern "C" int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch) {
+extern "C" int krea2_shard_advance(krea2_stream stream, uint32_t *epoch_base, uint32_t delta) {
+    clear_error();
+    KREA2_REQUIRE(epoch_base, "shard_advance: epoch word is null");
+    shard_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch_base, delta);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(KREA2_RUNTIME, "shard_advance launch failed: %s", cudaGetErrorString(status));
+    return KREA2_OK;
+}
+
+extern "C" int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world, uint32_t epoch,
+                                const uint32_t *epoch_base) {
     clear_error();
     KREA2_REQUIRE(flags && world >= 1 && world <= 8, "shard_wait: flags null or world outside 1..8");
-    shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch);
+    shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, epoch_base);
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "shard_wait launch failed: %s", cudaGetErrorString(status));
     return KREA2_OK;

@@ -168,6 +168,8 @@ class TensorParallel:
         self.attn_gu = fabric.allocate("attn_gu", rank, (cap, wide), torch.float16)
         self.flags = fabric.allocate("flags", rank, (8,), torch.int32)
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.epoch_base = torch.zeros(1, dtype=torch.int32, device="cuda")  # advanced once per forward
+        self.graph = None
         self.a_q = torch.zeros((cap, shape.gemm_pitch(wide)), dtype=torch.int8, device="cuda")
         self.a_s = torch.zeros(cap, dtype=torch.float32, device="cuda")
         self.epoch = 0
@@ -187,6 +189,7 @@ class TensorParallel:
             self.epoch += 1
             desc.epoch = self.epoch
             desc.counter = self.counter.data_ptr()
+            desc.epoch_base = self.epoch_base.data_ptr()
         else:  # the slab goes to the local copy only; a collective moves it afterwards
             desc.world, desc.rank = 1, 0
             desc.dest[0] = getattr(self, out_name).data_ptr()
@@ -199,7 +202,8 @@ class TensorParallel:
         self.launches += 1
 
     def _wait(self) -> None:
-        check(lib().krea2_shard_wait(self.stream.cuda_stream, self.flags.data_ptr(), self.world, self.epoch))
+        check(lib().krea2_shard_wait(self.stream.cuda_stream, self.flags.data_ptr(), self.world, self.epoch,
+                                     self.epoch_base.data_ptr()))
 
     def _gather(self, out_name: str, n_total: int, swiglu: bool) -> None:
         """The NCCL baseline: all-gather of the column slabs, then a repack into row-major."""
@@ -226,6 +230,7 @@ class TensorParallel:
             elif self.world > 1:
                 self._gather(name, n_total, swiglu)
 
+        self.epoch = 0  # epochs are relative to *epoch_base, which moves on at the end of the forward
         for i, w in enumerate(self.shards):
             m = mods[i]
             ops.prepare_norm_i8(self.x[:t], w.prenorm, m[0], m[1], self.a_q, self.a_s, h, self.ph, 1e-5, st)
@@ -248,12 +253,35 @@ class TensorParallel:
             self._sharded(RESID, w.down_q, w.down_s, m[5], inter, self.pi, h, "x", h, collective)
             yield
             after_gemm("x", h)
+        if collective == "fused":
+            check(lib().krea2_shard_advance(st.cuda_stream, self.epoch_base.data_ptr(), self.epoch))
 
     def forward(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused") -> torch.Tensor:
         """x: device bf16 [tokens][hidden] (the same on every rank); returns the new residual stream."""
         self.x[: self.tokens].copy_(x)
         for _ in self.stages(mods, collective):
             pass
+        return self.x[: self.tokens]
+
+    def forward_graph(self, x: torch.Tensor, mods: torch.Tensor) -> torch.Tensor:
+        """The fused forward replayed from a CUDA graph recorded on first use (the inputs are copied
+        into fixed buffers, as Session.run_device does).  Every rank must call it the same number of
+        times: the flags count forwards."""
+        if self.graph is None:
+            self._mods = mods.clone()
+            capture = torch.cuda.Stream()
+            capture.wait_stream(torch.cuda.current_stream())
+            saved = self.stream
+            self.stream = capture
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=capture):
+                for _ in self.stages(self._mods, "fused"):
+                    pass
+            self.stream = saved
+            self.graph = graph
+        self._mods.copy_(mods)
+        self.x[: self.tokens].copy_(x)
+        self.graph.replay()
         return self.x[: self.tokens]
 
 

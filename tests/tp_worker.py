@@ -55,8 +55,8 @@ def main():
         want = x_dev.clone()
         single.run_device(stream, want, mods_dev, torch.from_numpy(cos), torch.from_numpy(sin))
         torch.cuda.synchronize()
-        for collective in ("fused", "nccl", "fused"):
-            out = tp.forward(x_dev, mods_dev, collective)
+        for collective in ("fused", "nccl", "fused", "graph", "graph"):
+            out = tp.forward_graph(x_dev, mods_dev) if collective == "graph" else tp.forward(x_dev, mods_dev, collective)
             fabric.barrier()
             if not np.array_equal(bits(out), bits(want)):
                 print(f"rank {rank}: {collective} result differs", flush=True)
@@ -84,9 +84,10 @@ def main():
         base = timed(lambda: single.run_device(stream, x_dev.clone(), mods_dev, torch.from_numpy(cos), torch.from_numpy(sin)))
         fused = timed(lambda: tp.forward(x_dev, mods_dev, "fused"))
         nccl = timed(lambda: tp.forward(x_dev, mods_dev, "nccl"))
+        graph = timed(lambda: tp.forward_graph(x_dev, mods_dev))
         if rank == 0:
-            print({"world": world, "layers": layers, "tokens": tokens, "single_gpu_ms": base, "tp_fused_ms": fused,
-                   "tp_nccl_ms": nccl}, flush=True)
+            print({"world": world, "layers": layers, "tokens": tokens, "single_gpu_ms": base, "tp_fused_eager_ms": fused,
+                   "tp_nccl_eager_ms": nccl, "tp_fused_graph_ms": graph}, flush=True)
     single.close()
     dist.destroy_process_group()
 
