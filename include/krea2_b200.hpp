@@ -1,0 +1,167 @@
+// C++ face of the krea2_b200 C ABI (krea2_b200.h), shaped like the Rust crate it stands in for:
+// krea2::kernels::shape (src/kernels/shape.rs), krea2::kernels::Scalars (src/kernels/mod.rs:106-166),
+// krea2::Error (src/error.rs:10-29), krea2::session::{Weights, Session} (src/session/mod.rs).
+// Header-only; link against libkrea2_b200.so.
+#pragma once
+
+#include <array>
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "krea2_b200.h"
+
+namespace krea2 {
+
+// One class per variant of the crate's Error enum.
+struct Error : std::runtime_error {
+    krea2_status status;
+    Error(krea2_status s, const std::string &what) : std::runtime_error(what), status(s) {}
+};
+struct InvalidArgument : Error { explicit InvalidArgument(const std::string &w) : Error(KREA2_INVALID_ARGUMENT, w) {} };
+struct Cancelled : Error { explicit Cancelled(const std::string &w) : Error(KREA2_CANCELLED, w) {} };
+struct Poisoned : Error { explicit Poisoned(const std::string &w) : Error(KREA2_POISONED, w) {} };
+struct Runtime : Error { explicit Runtime(const std::string &w) : Error(KREA2_RUNTIME, w) {} };
+struct Internal : Error { explicit Internal(const std::string &w) : Error(KREA2_INTERNAL, w) {} };
+
+inline void check(int status) {
+    if (status == KREA2_OK) return;
+    const std::string what = krea2_last_error();
+    switch (status) {
+        case KREA2_INVALID_ARGUMENT: throw InvalidArgument(what);
+        case KREA2_CANCELLED: throw Cancelled(what);
+        case KREA2_POISONED: throw Poisoned(what);
+        case KREA2_RUNTIME: throw Runtime(what);
+        default: throw Internal(what);
+    }
+}
+
+namespace kernels {
+namespace shape {
+inline std::pair<std::size_t, std::size_t> tokens() { return {krea2_shape_tokens_min(), krea2_shape_tokens_max()}; }
+inline std::size_t capacity(std::size_t tokens) { return krea2_shape_capacity(tokens); }
+inline std::size_t attention_rows(std::size_t tokens) { return krea2_shape_attention_rows(tokens); }
+inline std::size_t gemm_pitch(std::size_t k) { return krea2_shape_gemm_pitch(k); }
+inline std::size_t gemm_grid_rows(std::size_t tokens) { return krea2_shape_gemm_grid_rows(tokens); }
+inline bool gemm_schedule_rows(std::size_t tokens) { return krea2_shape_gemm_schedule_rows(tokens) != 0; }
+constexpr std::size_t GEMM_ROWS = 256;
+inline std::size_t gemm_m_group() { return krea2_shape_gemm_m_group(); }
+enum class GemmTile { Narrow, Wide };
+inline GemmTile gemm_tile(const char *stem) {
+    return krea2_shape_gemm_tile_columns(stem) == 256 ? GemmTile::Wide : GemmTile::Narrow;
+}
+inline std::size_t columns(GemmTile tile) { return tile == GemmTile::Wide ? 256 : 128; }
+inline std::uint32_t threads(GemmTile tile) { return tile == GemmTile::Wide ? 512 : 256; }
+inline const char *gemm_source(const char *family, GemmTile tile) {
+    return krea2_shape_gemm_source(family, tile == GemmTile::Wide ? "gemm_down" : "gemm_wo");
+}
+}  // namespace shape
+
+// Up to four indices, then up to eight floats (src/kernels/mod.rs:106-135).
+class Scalars {
+public:
+    Scalars index(std::size_t value) const {
+        if (index_count_ >= 4) throw Internal("a kernel takes at most four indices");
+        Scalars next = *this;
+        next.indices_[next.index_count_++] = value;
+        return next;
+    }
+    Scalars scalar(float value) const {
+        if (float_count_ >= 8) throw Internal("a kernel takes at most eight floats");
+        Scalars next = *this;
+        next.floats_[next.float_count_++] = value;
+        return next;
+    }
+    const std::uint64_t *indices() const { return indices_.data(); }
+    std::size_t index_count() const { return index_count_; }
+
+private:
+    std::array<std::uint64_t, 4> indices_{};
+    std::array<float, 8> floats_{};
+    std::size_t index_count_ = 0, float_count_ = 0;
+};
+
+// kernels::grid (src/kernels/mod.rs:77-84).
+inline std::array<std::uint32_t, 3> grid(const char *stage, std::size_t x, std::size_t y) {
+    if (x > 0xffffffffull || y > 0xffffffffull)
+        throw Internal(std::string(stage) + ": " + std::to_string(x > y ? x : y) + " workgroups exceed the grid");
+    return {static_cast<std::uint32_t>(x), static_cast<std::uint32_t>(y), 1u};
+}
+}  // namespace kernels
+
+namespace ops {
+// Ops::launch (src/ops/mod.rs:673-693).
+inline void launch(krea2_stream stream, const char *name, const std::vector<krea2_config_entry> &config,
+                   const kernels::Scalars &scalars, const std::vector<krea2_binding> &bindings, std::size_t grid_x,
+                   std::size_t grid_y, std::uint32_t threads) {
+    kernels::grid(name, grid_x, grid_y);
+    check(krea2_launch(stream, name, config.data(), config.size(), scalars.indices(), scalars.index_count(),
+                       bindings.data(), bindings.size(), grid_x, grid_y, threads));
+}
+// Ops::launch_1d (:701-713).
+inline void launch_1d(krea2_stream stream, const char *name, const std::vector<krea2_config_entry> &config,
+                      const kernels::Scalars &scalars, const std::vector<krea2_binding> &bindings,
+                      std::size_t elements) {
+    launch(stream, name, config, scalars, bindings, (elements + 255) / 256, 1, 256);
+}
+}  // namespace ops
+
+namespace session {
+constexpr std::size_t HIDDEN = 6144, KV_HEADS = 12, HEAD_DIM = 128, INTER = 16384;       // src/session/mod.rs:35-41
+constexpr std::size_t QKVG = HIDDEN + 2 * KV_HEADS * HEAD_DIM + HIDDEN;                   // :43
+constexpr std::size_t GATE_OFFSET = HIDDEN + 2 * KV_HEADS * HEAD_DIM;                     // :45
+
+class Weights {
+public:
+    Weights(const krea2_dims &dims, std::size_t layers) { check(krea2_weights_create(&dims, layers, &handle_)); }
+    Weights(const Weights &other) : handle_(other.handle_) { krea2_weights_retain(handle_); }  // Arc<Weights>
+    Weights &operator=(const Weights &) = delete;
+    ~Weights() { krea2_weights_release(handle_); }
+    void fill_synthetic(std::uint64_t seed, krea2_stream stream) { check(krea2_weights_fill_synthetic(handle_, seed, stream)); }
+    std::pair<void *, std::size_t> locate(const char *name) const {
+        void *ptr = nullptr;
+        std::size_t bytes = 0;
+        check(krea2_weights_locate(handle_, name, &ptr, &bytes));
+        return {ptr, bytes};
+    }
+    krea2_weights *raw() const { return handle_; }
+
+private:
+    krea2_weights *handle_ = nullptr;
+};
+
+class Session {
+public:
+    static void validate_dimensions(std::size_t tokens, std::size_t layers) {
+        check(krea2_session_validate_dimensions(tokens, layers));
+    }
+    // Session::with_weights (src/session/mod.rs:265-276).
+    Session(krea2_stream stream, const Weights &weights, std::size_t tokens, std::size_t layers) {
+        check(krea2_session_create(stream, weights.raw(), tokens, layers, &handle_));
+    }
+    Session(const Session &) = delete;
+    Session &operator=(const Session &) = delete;
+    ~Session() { krea2_session_destroy(handle_); }
+    std::size_t tokens() const { return krea2_session_tokens(handle_); }
+    std::size_t layers() const { return krea2_session_layers(handle_); }
+    bool set_profile(bool enable) { return krea2_session_set_profile(handle_, enable ? 1 : 0) != 0; }
+    // Session::run (:502-540): host buffers; block_count 0 = to the last layer.
+    void run(krea2_stream stream, std::uint16_t *x, const float *mods, const float *cos, const float *sin,
+             std::size_t first_block = 0, std::size_t block_count = 0) {
+        check(krea2_session_run(handle_, stream, x, mods, cos, sin, first_block, block_count));
+    }
+    // Session::run_device (:553-588): device x and mods, graph replay.
+    void run_device(krea2_stream stream, void *x, std::size_t x_bytes, const void *mods, std::size_t mods_bytes,
+                    const float *cos, const float *sin) {
+        check(krea2_session_run_device(handle_, stream, x, x_bytes, mods, mods_bytes, cos, sin));
+    }
+
+private:
+    krea2_session *handle_ = nullptr;
+};
+}  // namespace session
+
+}  // namespace krea2

@@ -173,3 +173,15 @@ def test_generic_launch_checks_names_counts_and_geometry():
     assert status == 1 and "buffer 1 spans 100 bytes" in msg
     status, msg = launch("prepare_plain_i8", {"width": 2048, "out_stride": 2048}, 3, [1 << 14] * 3, 4, 1, 256)
     assert status == 1 and "grid" in msg
+
+
+def test_cpp_host_mirror_compiles_and_agrees(tmp_path):
+    """include/krea2_b200.hpp (the C++ face shaped like the crate's modules) against the same rules."""
+    import subprocess
+    exe = tmp_path / "host_mirror"
+    lib_dir = os.path.join(ROOT, "krea2_hrx_b200")
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "host_mirror.cpp"), "-o", str(exe), "-L", lib_dir, "-lkrea2_b200",
+                    f"-Wl,-rpath,{lib_dir}"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and "host mirror ok" in out.stdout, out.stdout + out.stderr
