@@ -102,6 +102,34 @@ int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const void *a, const
 int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
                       size_t k_size, size_t k_stride, size_t n_size);
 
+/* ---------------------------------------------------------------- the rest of a block
+ * The three launches between the q|k|v|gate GEMM and the gated prologue
+ * (src/session/mod.rs:714-755).  Not W8A8 products; they make a session forward a real block. */
+
+/* kernels/rope_qknorm_f16.loom:13-27.  qkv f16 [tokens][row_stride] (q heads at column 0, k heads
+ * at k_offset, v heads right after k); q_scale, k_scale f32 [128]; cos, sin f32 [tokens][128];
+ * q_out f16 [tokens][q_heads*128], k_out and v_out f16 [tokens][kv_heads*128]. */
+int krea2_rope_qknorm_f16(krea2_stream stream, size_t tokens, const void *qkv, const float *q_scale,
+                          const float *k_scale, const float *cos_table, const float *sin_table, void *q_out,
+                          void *k_out, void *v_out, size_t row_stride, size_t q_heads, size_t kv_heads,
+                          size_t k_offset, float eps);
+
+/* kernels/native/v_transpose.loom.  x f16 [rows][width] -> out f16 [width][row_capacity]; columns
+ * rows..row_capacity of `out` are left as they are except inside the last 32-row tile, where
+ * they are written as zero. */
+int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x, void *out, size_t width, size_t row_capacity);
+
+/* kernels/attention_gqa_lds_f16_wmma.loom:18-41 (and the _q32 sibling, the same function on
+ * 32-row groups).  q f16 [tokens][q_stride], k f16 [tokens][kv_stride], v_transposed f16
+ * [kv_stride][token_capacity] with finite (zero) headroom past `tokens`, out f16
+ * [tokens][out_stride]; query head h reads key/value head h / (q_stride / kv_stride). */
+int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
+                                     const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                     size_t kv_stride, size_t out_stride, size_t token_capacity, float scale);
+int krea2_attention_gqa_lds_f16_wmma_q32(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
+                                         const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                         size_t kv_stride, size_t out_stride, size_t token_capacity, float scale);
+
 /* ---------------------------------------------------------------- column-sharded GEMMs
  * New with this library (the reference runs on one device).  Device r of `world` holds rows
  * [r*N/world, (r+1)*N/world) of a weight and its scales, computes the matching column slab of

@@ -77,6 +77,11 @@ SIGNATURES = {
     "krea2_gemm_i8_swiglu_256": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                          c_size_t, c_size_t, c_size_t]),
     "krea2_gemm_i8_acc": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
+    "krea2_rope_qknorm_f16": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
+    "krea2_v_transpose": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_size_t]),
+    "krea2_attention_gqa_lds_f16_wmma": (c_int, [c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
+    "krea2_attention_gqa_lds_f16_wmma_q32": (c_int, [c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
     "krea2_gemm_i8_sharded": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                       c_size_t, c_size_t, POINTER(Shard)]),
     "krea2_shard_wait": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),

@@ -1,0 +1,603 @@
+// The three launches that sit between the q|k|v|gate GEMM and the gated prologue of a block
+// (src/session/mod.rs:714-755): per-head QK-norm with rotary embedding, the V transpose, and
+// grouped-query fp16 attention.  They are not W8A8 products; they complete the block so that
+// a forward of the session is a real transformer block chain.
+//
+//   krea2_rope_qknorm_f16            kernels/rope_qknorm_f16.loom
+//   krea2_v_transpose                kernels/native/v_transpose.loom
+//   krea2_attention_gqa_lds_f16_wmma kernels/attention_gqa_lds_f16_wmma.loom (and the _q32 sibling,
+//                                    which computes the same function on 32-row groups)
+//
+// Attention is a flash-attention forward on the fifth-generation tensor cores: one CTA per
+// (128 query rows, query head); S = Q K^T and O += P V are tcgen05.mma kind::f16 with f32
+// accumulators in tensor memory, K and V^T tiles of 128 keys arrive by TMA (128-byte swizzle,
+// two stages each), four softmax warps read S from tensor memory (one query row per thread),
+// keep the running maximum and sum in registers and hand P to the second product through shared
+// memory.  O stays in tensor memory across key tiles; it is rescaled there only when a row's
+// maximum moves by more than 2^8 (the reference maximum used for the exponentials is otherwise
+// left stale, which changes neither O nor the sum's ratio).  S is double-buffered so that the
+// next tile's Q K^T runs under the current tile's softmax.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace krea2 {
+namespace {
+
+constexpr unsigned kFull = 0xffffffffu;
+
+// ---------------------------------------------------------------- rope + qk norm
+// One 256-thread block per token, a warp per head, four channels per lane
+// (kernels/rope_qknorm_f16.loom:78-157).  The two sums the reference leaves unordered are fixed
+// as ((s0+s1)+(s2+s3)) per lane and the xor butterfly 16..1 across the warp; rsqrt is 1/sqrt.
+__global__ void __launch_bounds__(256)
+rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q_scale,
+                   const float *__restrict__ k_scale, const float *__restrict__ cos_table,
+                   const float *__restrict__ sin_table, uint16_t *__restrict__ q_out, uint16_t *__restrict__ k_out,
+                   uint16_t *__restrict__ v_out, uint32_t row_stride, uint32_t q_heads, uint32_t kv_heads,
+                   uint32_t k_offset, float eps) {
+    const size_t row = blockIdx.x;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = lane * 4;
+    const uint32_t heads_total = q_heads + 2 * kv_heads;
+    const float4 cs = __ldg(reinterpret_cast<const float4 *>(cos_table + row * 128 + col));
+    const float4 sn = __ldg(reinterpret_cast<const float4 *>(sin_table + row * 128 + col));
+    for (uint32_t head = warp; head < heads_total; head += 8) {
+        const bool is_q = head < q_heads, is_v = head >= q_heads + kv_heads;
+        const uint32_t base = is_q ? head * 128 : k_offset + (head - q_heads) * 128;  // v follows k in the row
+        const uint2 raw = *reinterpret_cast<const uint2 *>(qkv + row * row_stride + base + col);
+        if (is_v) {
+            *reinterpret_cast<uint2 *>(v_out + row * (kv_heads * 128) + (head - q_heads - kv_heads) * 128 + col) = raw;
+            continue;
+        }
+        const __half2 lo = *reinterpret_cast<const __half2 *>(&raw.x), hi = *reinterpret_cast<const __half2 *>(&raw.y);
+        const float v0 = __low2float(lo), v1 = __high2float(lo), v2 = __low2float(hi), v3 = __high2float(hi);
+        float ss = __fadd_rn(__fadd_rn(__fmul_rn(v0, v0), __fmul_rn(v1, v1)), __fadd_rn(__fmul_rn(v2, v2), __fmul_rn(v3, v3)));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(kFull, ss, off));
+        const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, 0.0078125f), eps)));
+        const float4 sc = __ldg(reinterpret_cast<const float4 *>((is_q ? q_scale : k_scale) + col));
+        // x = bf16((h * rinv) * (1 + scale)); out = bf16(x * cos + rot * sin), rot = (-x1, x0, -x3, x2)
+        const float x0 = bf_round(__fmul_rn(__fmul_rn(v0, rinv), __fadd_rn(sc.x, 1.0f)));
+        const float x1 = bf_round(__fmul_rn(__fmul_rn(v1, rinv), __fadd_rn(sc.y, 1.0f)));
+        const float x2 = bf_round(__fmul_rn(__fmul_rn(v2, rinv), __fadd_rn(sc.z, 1.0f)));
+        const float x3 = bf_round(__fmul_rn(__fmul_rn(v3, rinv), __fadd_rn(sc.w, 1.0f)));
+        const float o0 = bf_round(__fadd_rn(__fmul_rn(x0, cs.x), __fmul_rn(__fsub_rn(0.0f, x1), sn.x)));
+        const float o1 = bf_round(__fadd_rn(__fmul_rn(x1, cs.y), __fmul_rn(x0, sn.y)));
+        const float o2 = bf_round(__fadd_rn(__fmul_rn(x2, cs.z), __fmul_rn(__fsub_rn(0.0f, x3), sn.z)));
+        const float o3 = bf_round(__fadd_rn(__fmul_rn(x3, cs.w), __fmul_rn(x2, sn.w)));
+        const __half2 out_lo = __floats2half2_rn(o0, o1), out_hi = __floats2half2_rn(o2, o3);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t *>(&out_lo);
+        packed.y = *reinterpret_cast<const uint32_t *>(&out_hi);
+        uint16_t *dst = is_q ? q_out + row * (q_heads * 128) + head * 128 : k_out + row * (kv_heads * 128) + (head - q_heads) * 128;
+        *reinterpret_cast<uint2 *>(dst + col) = packed;
+    }
+}
+
+// ---------------------------------------------------------------- v transpose
+// x [rows][width] -> out [width][capacity], 32 x 32 tiles through shared memory; columns past
+// `rows` inside a tile are written as zero (kernels/native/v_transpose.loom).
+__global__ void __launch_bounds__(256)
+v_transpose_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out, uint32_t rows, uint32_t width,
+                   uint32_t capacity) {
+    __shared__ uint16_t tile[32][34];
+    const uint32_t row0 = blockIdx.x * 32, col0 = blockIdx.y * 32;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t r = row0 + ty + 8 * i;
+        tile[ty + 8 * i][tx] = r < rows ? x[static_cast<size_t>(r) * width + col0 + tx] : uint16_t(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t c = col0 + ty + 8 * i, r = row0 + tx;
+        if (r < capacity) out[static_cast<size_t>(c) * capacity + r] = tile[tx][ty + 8 * i];
+    }
+}
+
+// ---------------------------------------------------------------- attention
+constexpr int kTile = 128;            // query rows per CTA, keys per step, channels per head
+constexpr int kSubtileBytes = 16384;  // [128 rows][64 f16]: one 128-byte swizzled column block
+constexpr int kOperandBytes = 2 * kSubtileBytes;
+constexpr int kAttnThreads = 192;     // warps 0-3 softmax, 4 TMA, 5 MMA
+constexpr int kSoftmaxWarps = 4;
+constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
+constexpr int kAttnSmemBytes = 6 * kOperandBytes + 1024 + 256;  // Q, K x2, V x2, P
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ int g_attention_status = 0;  // folded into krea2_device_status by take_attention_status
+constexpr int kAttentionTimedOut = 32;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = timer_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (timer_ns() - start > kAttnWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(&g_attention_status, kAttentionTimedOut);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t address, float (&r)[32]) {
+    uint32_t *u = reinterpret_cast<uint32_t *>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+          "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+          "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(address));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t address, const float (&r)[32]) {
+    const uint32_t *u = reinterpret_cast<const uint32_t *>(r);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(address),
+        "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]),
+        "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]),
+        "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]),
+        "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand tile of 128-byte swizzled rows, eight rows per 1024-byte atom (as in the GEMM).
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+    return static_cast<uint64_t>((address & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// kind::f16 with f16 operands, f32 accumulate (1 at bit 4), both K-major, N/8 at bit 17, M/16 at bit 24.
+constexpr uint32_t kIdescF16 = (1u << 4) | (static_cast<uint32_t>(kTile >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
+
+struct AttnArgs {
+    uint32_t tokens, q_heads_per_kv, out_stride;
+    float scale_log2;  // softmax scale times log2(e)
+    uint16_t *out;
+};
+
+// One 128 x 128 x 128 product from two 64-wide K-major subtiles per operand: 8 instructions of K = 16.
+__device__ __forceinline__ void issue_product(uint32_t tmem_d, uint32_t a_addr, uint32_t b_addr, bool accumulate) {
+#pragma unroll
+    for (int sub = 0; sub < 2; sub++) {
+        const uint64_t a_desc = smem_descriptor(a_addr + sub * kSubtileBytes);
+        const uint64_t b_desc = smem_descriptor(b_addr + sub * kSubtileBytes);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            umma_f16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, kIdescF16, (accumulate || sub != 0 || k != 0) ? 1u : 0u);
+    }
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const AttnArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_smem = smem, *k_smem = smem + kOperandBytes, *v_smem = smem + 3 * kOperandBytes;
+    uint8_t *p_smem = smem + 5 * kOperandBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 6 * kOperandBytes);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *p_empty = bars + 14, *o_done = bars + 15;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q0 = blockIdx.x * kTile, head = blockIdx.y, kv_head = head / g.q_heads_per_kv;
+    const uint32_t tiles = (g.tokens + kTile - 1) / kTile;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(k_full + s, 1);
+            mbar_init(k_empty + s, 1);
+            mbar_init(v_full + s, 1);
+            mbar_init(v_empty + s, 1);
+            mbar_init(s_full + s, 1);
+            mbar_init(s_empty + s, kSoftmaxWarps);
+        }
+        mbar_init(p_full, kSoftmaxWarps);
+        mbar_init(p_empty, 1);
+        mbar_init(o_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 2 * kTile;  // S buffers at columns 0 and 128, O at 256
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kOperandBytes);
+            tma_load_2d(q_smem, &map_q, q_full, static_cast<int>(head * kTile), static_cast<int>(q0));
+            tma_load_2d(q_smem + kSubtileBytes, &map_q, q_full, static_cast<int>(head * kTile + 64), static_cast<int>(q0));
+            for (uint32_t j = 0; j < tiles; j++) {
+                const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+                const int key0 = static_cast<int>(j * kTile);
+                if (!mbar_wait(k_empty + s, phase ^ 1u, abort_flag)) break;
+                mbar_expect_tx(k_full + s, kOperandBytes);
+                uint8_t *k_dst = k_smem + s * kOperandBytes;
+                tma_load_2d(k_dst, &map_k, k_full + s, static_cast<int>(kv_head * kTile), key0);
+                tma_load_2d(k_dst + kSubtileBytes, &map_k, k_full + s, static_cast<int>(kv_head * kTile + 64), key0);
+                if (!mbar_wait(v_empty + s, phase ^ 1u, abort_flag)) break;
+                mbar_expect_tx(v_full + s, kOperandBytes);
+                uint8_t *v_dst = v_smem + s * kOperandBytes;
+                tma_load_2d(v_dst, &map_v, v_full + s, key0, static_cast<int>(kv_head * kTile));
+                tma_load_2d(v_dst + kSubtileBytes, &map_v, v_full + s, key0 + 64, static_cast<int>(kv_head * kTile));
+            }
+            if (*abort_flag) {
+                const uint64_t start = timer_ns();
+                while (timer_ns() - start < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            bool alive = mbar_wait(q_full, 0, abort_flag);
+            tc_fence_after();
+            const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+            for (uint32_t j = 0; alive && j <= tiles; j++) {
+                if (j < tiles) {  // S_j = Q K_j^T into S buffer j & 1
+                    const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+                    if (!mbar_wait(k_full + s, phase, abort_flag) || !mbar_wait(s_empty + s, phase ^ 1u, abort_flag)) break;
+                    tc_fence_after();
+                    issue_product(tmem_base + s * kTile, q_addr, smem_u32(k_smem + s * kOperandBytes), false);
+                    umma_commit(s_full + s);
+                    umma_commit(k_empty + s);
+                }
+                if (j > 0) {  // O += P_{j-1} V_{j-1}
+                    const uint32_t i = j - 1, s = i & 1u, phase = (i >> 1) & 1u;
+                    if (!mbar_wait(p_full, i & 1u, abort_flag) || !mbar_wait(v_full + s, phase, abort_flag)) break;
+                    tc_fence_after();
+                    issue_product(tmem_o, p_addr, smem_u32(v_smem + s * kOperandBytes), i > 0);
+                    umma_commit(p_empty);
+                    umma_commit(v_empty + s);
+                    if (j == tiles) umma_commit(o_done);
+                }
+            }
+        }
+    } else {
+        // Softmax warps: warp w owns TMEM lanes 32w..32w+31 = query rows q0 + 32w + lane.
+        const uint32_t lane_bits = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t row_in_tile = warp * 32 + lane;
+        float reference = -INFINITY, sum = 0.0f;  // in units of log2: scores are scaled by scale * log2(e)
+        bool alive = true;
+        for (uint32_t j = 0; j < tiles; j++) {
+            const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+            const bool ready = mbar_wait(s_full + s, phase, abort_flag);
+            if (!__all_sync(kFull, ready)) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = tmem_base + s * kTile + lane_bits;
+            const uint32_t valid = g.tokens - j * kTile;  // keys of this tile before the end of the sequence
+            // pass 1: the row's maximum over this tile's valid keys
+            float tile_max = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                float v[32];
+                tmem_load_32(s_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (static_cast<uint32_t>(c * 32 + i) < valid) tile_max = fmaxf(tile_max, v[i]);
+            }
+            tile_max *= g.scale_log2;
+            // The exponent reference moves only when the maximum has grown by more than 2^8.
+            float alpha = 1.0f;
+            const bool move = tile_max > reference + 8.0f;
+            if (move) {
+                alpha = fast_exp2(reference - tile_max);  // 0 on the first tile
+                reference = tile_max;
+                sum *= alpha;
+            }
+            // P and O of the previous tile must be consumed before P is overwritten and O rescaled.
+            if (j > 0) {
+                const bool consumed = mbar_wait(p_empty, (j - 1) & 1u, abort_flag);
+                if (!__all_sync(kFull, consumed)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                if (__any_sync(kFull, move)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_load_32(tmem_o + lane_bits + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] *= alpha;
+                        tmem_store_32(tmem_o + lane_bits + c * 32, o);
+                    }
+                }
+            }
+            // pass 2: p = 2^(score - reference), f16, into the K-major swizzled P tile
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                float v[32];
+                tmem_load_32(s_addr + c * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = static_cast<uint32_t>(c * 32 + i) < valid ? fast_exp2(fmaf(v[i], g.scale_log2, -reference)) : 0.0f;
+                    float p1 = static_cast<uint32_t>(c * 32 + i + 1) < valid ? fast_exp2(fmaf(v[i + 1], g.scale_log2, -reference)) : 0.0f;
+                    sum += p0 + p1;
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    packed[i / 2] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key subtile row
+                uint8_t *row_base = p_smem + (c >> 1) * kSubtileBytes + row_in_tile * 128;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int chunk = (c & 1) * 4 + q;
+                    *reinterpret_cast<uint4 *>(row_base + ((chunk ^ (row_in_tile & 7)) * 16)) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty + s);
+                mbar_arrive(p_full);
+            }
+        }
+        if (alive) {
+            const bool finished = mbar_wait(o_done, 0, abort_flag);
+            if (__all_sync(kFull, finished)) {
+                tc_fence_after();
+                const uint32_t row = q0 + row_in_tile;
+                const float inv = 1.0f / sum;
+                uint16_t *dst = g.out + static_cast<size_t>(row) * g.out_stride + head * kTile;
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_load_32(tmem_o + lane_bits + c * 32, o);
+                    if (row < g.tokens) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const __half2 h = __floats2half2_rn(o[8 * q + 2 * i] * inv, o[8 * q + 2 * i + 1] * inv);
+                                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+                            }
+                            *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+// f16 [rows][pitch] as a 2-D tensor (inner x rows) with boxes of 64 x 128 elements, 128-byte swizzle.
+int make_f16_map(CUtensorMap *map, const void *base, size_t inner, size_t rows, size_t pitch) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, element_strides,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+    return KREA2_OK;
+}
+
+int launch_check(const char *what) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(KREA2_RUNTIME, "%s launch failed: %s", what, cudaGetErrorString(status));
+    return KREA2_OK;
+}
+
+int ensure_attention() {
+    static std::once_flag once[64];
+    static cudaError_t attr_status[64];
+    int device = 0;
+    KREA2_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
+    std::call_once(once[device], [&] {
+        attr_status[device] =
+            cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
+    });
+    if (attr_status[device] != cudaSuccess)
+        return fail(KREA2_RUNTIME, "cannot reserve %d bytes of shared memory: %s", kAttnSmemBytes,
+                    cudaGetErrorString(attr_status[device]));
+    return encode_tiled() ? KREA2_OK : fail(KREA2_RUNTIME, "cuTensorMapEncodeTiled is not available from this driver");
+}
+
+}  // namespace
+
+int prepare_attention_device() { return ensure_attention(); }
+
+// Reads and clears the attention kernel's status word (the device is already synchronised).
+int take_attention_status(int *value) {
+    KREA2_CUDA(cudaMemcpyFromSymbol(value, g_attention_status, sizeof(int)));
+    if (*value != 0) {
+        int zero = 0;
+        KREA2_CUDA(cudaMemcpyToSymbol(g_attention_status, &zero, sizeof(int)));
+    }
+    return KREA2_OK;
+}
+
+}  // namespace krea2
+
+using namespace krea2;
+
+extern "C" int krea2_rope_qknorm_f16(krea2_stream stream, size_t tokens, const void *qkv, const float *q_scale,
+                                     const float *k_scale, const float *cos_table, const float *sin_table, void *q_out,
+                                     void *k_out, void *v_out, size_t row_stride, size_t q_heads, size_t kv_heads,
+                                     size_t k_offset, float eps) {
+    clear_error();
+    KREA2_REQUIRE(tokens >= 1 && tokens <= 1048576, "rope_qknorm_f16: tokens %zu outside 1..1048576", tokens);
+    KREA2_REQUIRE(row_stride >= 128 && row_stride <= 65536 && row_stride % 128 == 0,
+                  "rope_qknorm_f16: row_stride %zu must be a multiple of 128 up to 65536", row_stride);
+    KREA2_REQUIRE(q_heads >= 1 && q_heads <= 256 && kv_heads >= 1 && kv_heads <= 256, "rope_qknorm_f16: heads outside 1..256");
+    KREA2_REQUIRE(k_offset >= 128 && k_offset % 128 == 0 && k_offset >= q_heads * 128 &&
+                      k_offset + 2 * kv_heads * 128 <= row_stride,
+                  "rope_qknorm_f16: k_offset %zu must be a multiple of 128 past the q heads with k and v inside the row",
+                  k_offset);
+    KREA2_REQUIRE(qkv && q_scale && k_scale && cos_table && sin_table && q_out && k_out && v_out, "rope_qknorm_f16: null buffer");
+    KREA2_REQUIRE(aligned16(qkv) && aligned16(q_scale) && aligned16(k_scale) && aligned16(cos_table) && aligned16(sin_table) &&
+                      aligned16(q_out) && aligned16(k_out) && aligned16(v_out),
+                  "rope_qknorm_f16: buffers must be 16-byte aligned");
+    rope_qknorm_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(qkv), q_scale, k_scale, cos_table, sin_table, static_cast<uint16_t *>(q_out),
+        static_cast<uint16_t *>(k_out), static_cast<uint16_t *>(v_out), static_cast<uint32_t>(row_stride),
+        static_cast<uint32_t>(q_heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(k_offset), eps);
+    return launch_check("rope_qknorm_f16");
+}
+
+extern "C" int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x, void *out, size_t width,
+                                 size_t row_capacity) {
+    clear_error();
+    KREA2_REQUIRE(width >= 32 && width <= 65536 && width % 32 == 0, "v_transpose: width %zu must be a multiple of 32", width);
+    KREA2_REQUIRE(row_capacity >= 32 && row_capacity <= 1048576 && row_capacity % 32 == 0,
+                  "v_transpose: row_capacity %zu must be a multiple of 32", row_capacity);
+    KREA2_REQUIRE(rows >= 1 && rows <= row_capacity, "v_transpose: rows %zu outside 1..row_capacity", rows);
+    KREA2_REQUIRE(x && out, "v_transpose: null buffer");
+    dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>(width / 32), 1);
+    v_transpose_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(x), static_cast<uint16_t *>(out), static_cast<uint32_t>(rows),
+        static_cast<uint32_t>(width), static_cast<uint32_t>(row_capacity));
+    return launch_check("v_transpose");
+}
+
+extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
+                                                const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                                size_t kv_stride, size_t out_stride, size_t token_capacity, float scale) {
+    clear_error();
+    KREA2_REQUIRE(tokens >= 16 && tokens <= 65536, "attention: tokens %zu outside 16..65536", tokens);
+    KREA2_REQUIRE(q_stride >= 128 && q_stride <= 32768 && q_stride % 128 == 0 && kv_stride >= 128 && kv_stride <= 32768 &&
+                      kv_stride % 128 == 0 && out_stride >= 128 && out_stride <= 32768 && out_stride % 128 == 0,
+                  "attention: strides must be multiples of 128 up to 32768");
+    KREA2_REQUIRE(kv_heads >= 1 && kv_heads * 128 == kv_stride, "attention: kv_heads %zu does not match kv_stride %zu", kv_heads,
+                  kv_stride);
+    KREA2_REQUIRE(q_stride % kv_stride == 0 && out_stride == q_stride,
+                  "attention: q heads must be a whole multiple of kv heads and out_stride must equal q_stride");
+    KREA2_REQUIRE(token_capacity >= 32 && token_capacity <= 1048576 && token_capacity % 16 == 0 && token_capacity >= tokens,
+                  "attention: token_capacity %zu must be a multiple of 16 and at least tokens", token_capacity);
+    KREA2_REQUIRE(scale == scale && scale > 0.0f, "attention: scale must be positive");
+    KREA2_REQUIRE(q && k && v_transposed && out && aligned16(q) && aligned16(k) && aligned16(v_transposed) && aligned16(out),
+                  "attention: buffers must be non-null and 16-byte aligned");
+    if (int status = ensure_attention()) return status;
+    CUtensorMap map_q, map_k, map_v;
+    if (int status = make_f16_map(&map_q, q, q_stride, tokens, q_stride)) return status;
+    if (int status = make_f16_map(&map_k, k, kv_stride, tokens, kv_stride)) return status;
+    if (int status = make_f16_map(&map_v, v_transposed, token_capacity, kv_stride, token_capacity)) return status;
+    AttnArgs args;
+    args.tokens = static_cast<uint32_t>(tokens);
+    args.q_heads_per_kv = static_cast<uint32_t>(q_stride / kv_stride);
+    args.out_stride = static_cast<uint32_t>(out_stride);
+    args.scale_log2 = scale * 1.4426950408889634f;
+    args.out = static_cast<uint16_t *>(out);
+    dim3 grid(static_cast<unsigned>((tokens + kTile - 1) / kTile), static_cast<unsigned>(q_stride / 128), 1);
+    attention_kernel<<<grid, kAttnThreads, kAttnSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, args);
+    return launch_check("attention");
+}
+
+extern "C" int krea2_attention_gqa_lds_f16_wmma_q32(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
+                                                    const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                                    size_t kv_stride, size_t out_stride, size_t token_capacity,
+                                                    float scale) {
+    return krea2_attention_gqa_lds_f16_wmma(stream, tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride, out_stride,
+                                            token_capacity, scale);
+}

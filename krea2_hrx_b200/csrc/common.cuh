@@ -34,6 +34,9 @@ void clear_error();
 
 // Defined with the GEMM: first-use initialisation done ahead of a stream capture.
 int prepare_gemm_device();
+// Defined with the attention kernel: the same for it, and its share of the device status word.
+int prepare_attention_device();
+int take_attention_status(int *value);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -1071,6 +1071,8 @@ extern "C" int krea2_device_status(int *host_status) {
         int zero = 0;
         KREA2_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
     }
-    *host_status = value;
+    int attention = 0;
+    if (int status = take_attention_status(&attention)) return status;
+    *host_status = value | attention;
     return KREA2_OK;
 }

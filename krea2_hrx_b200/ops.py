@@ -158,3 +158,24 @@ class Quantized:
         ops.launch_1d(stream, "lora_transport", kernels.config([("reverse", 2)]), one.index(out.numel()),
                       [out_f16, out], out.numel())
         return out
+
+
+# ------------------------------------------------------------------ the rest of a block
+def rope_qknorm_f16(qkv, q_scale, k_scale, cos, sin, q_out, k_out, v_out, row_stride, q_heads, kv_heads, k_offset,
+                    eps=1e-5, stream=None, tokens=None):
+    tokens = q_out.shape[0] if tokens is None else tokens
+    check(lib().krea2_rope_qknorm_f16(_stream_ptr(stream), tokens, qkv.data_ptr(), _ptr(q_scale), _ptr(k_scale), _ptr(cos),
+                                      _ptr(sin), _ptr(q_out), _ptr(k_out), _ptr(v_out), row_stride, q_heads, kv_heads,
+                                      k_offset, eps))
+
+
+def v_transpose(x, out, width, row_capacity, stream=None, rows=None):
+    rows = x.shape[0] if rows is None else rows
+    check(lib().krea2_v_transpose(_stream_ptr(stream), rows, _ptr(x), _ptr(out), width, row_capacity))
+
+
+def attention_gqa(tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride, out_stride, token_capacity, scale,
+                  stream=None, q32=False):
+    fn = lib().krea2_attention_gqa_lds_f16_wmma_q32 if q32 else lib().krea2_attention_gqa_lds_f16_wmma
+    check(fn(_stream_ptr(stream), tokens, kv_heads, _ptr(q), _ptr(k), _ptr(v_transposed), _ptr(out), q_stride, kv_stride,
+             out_stride, token_capacity, scale))

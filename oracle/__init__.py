@@ -185,3 +185,35 @@ def transport_f16_to_bf16(x):
     out = np.empty_like(x)
     lib().oracle_transport_f16_to_bf16(_p(x), _p(out), _sz(x.size))
     return out
+
+
+# ------------------------------------------------------------------ the rest of a block
+def rope_qknorm_f16(qkv, q_scale, k_scale, cos, sin, row_stride, q_heads, kv_heads, k_offset, eps=1e-5):
+    qkv = np.ascontiguousarray(qkv, dtype=np.uint16).reshape(-1, row_stride)
+    tokens = qkv.shape[0]
+    qs, ks, cos, sin = (np.ascontiguousarray(v, dtype=np.float32) for v in (q_scale, k_scale, cos, sin))
+    q = np.zeros((tokens, q_heads * 128), dtype=np.uint16)
+    k = np.zeros((tokens, kv_heads * 128), dtype=np.uint16)
+    v = np.zeros((tokens, kv_heads * 128), dtype=np.uint16)
+    lib().oracle_rope_qknorm_f16(_sz(tokens), _p(qkv), _p(qs), _p(ks), _p(cos), _p(sin), _p(q), _p(k), _p(v),
+                                 _sz(row_stride), _sz(q_heads), _sz(kv_heads), _sz(k_offset), ctypes.c_float(eps))
+    return q, k, v
+
+
+def v_transpose(x, width, capacity, out=None):
+    x = np.ascontiguousarray(x, dtype=np.uint16).reshape(-1, width)
+    out = np.zeros((width, capacity), dtype=np.uint16) if out is None else out
+    lib().oracle_v_transpose(_sz(x.shape[0]), _p(x), _p(out), _sz(width), _sz(capacity))
+    return out
+
+
+def attention_gqa(q, k, v, q_heads, kv_heads, scale):
+    """q [tokens][q_heads*128], k, v [tokens][kv_heads*128] as f16 bits -> f64 [tokens][q_heads*128]."""
+    q = np.ascontiguousarray(q, dtype=np.uint16)
+    queries = q.reshape(-1, q_heads * 128).shape[0]  # may be a subset of the rows: every query sees all keys
+    k, v = np.ascontiguousarray(k, dtype=np.uint16), np.ascontiguousarray(v, dtype=np.uint16)
+    tokens = k.reshape(-1, kv_heads * 128).shape[0]
+    out = np.zeros((queries, q_heads * 128), dtype=np.float64)
+    lib().oracle_attention_gqa(_sz(queries), _sz(tokens), _sz(q_heads), _sz(kv_heads), _p(q), _p(k), _p(v), _p(out),
+                               ctypes.c_double(scale))
+    return out

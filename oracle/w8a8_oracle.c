@@ -377,3 +377,84 @@ int oracle_threads(void) {
     return 1;
 #endif
 }
+
+/* ---------------------------------------------------------------- the rest of a block
+ * Not W8A8 products; restated so that the session's full block can be checked. */
+
+/* kernels/rope_qknorm_f16.loom:78-157.  Canonical orders for the two sums the reference leaves
+ * open: four squares per lane fold as (s0+s1)+(s2+s3), the 32 lanes by xor butterfly 16..1. */
+void oracle_rope_qknorm_f16(size_t tokens, const uint16_t *qkv, const float *q_scale, const float *k_scale,
+                            const float *cos_table, const float *sin_table, uint16_t *q_out, uint16_t *k_out,
+                            uint16_t *v_out, size_t row_stride, size_t q_heads, size_t kv_heads, size_t k_offset,
+                            float eps) {
+    for (size_t t = 0; t < tokens; t++) {
+        const uint16_t *row = qkv + t * row_stride;
+        memcpy(v_out + t * kv_heads * 128, row + k_offset + kv_heads * 128, kv_heads * 128 * 2);
+        for (size_t head = 0; head < q_heads + kv_heads; head++) {
+            int is_q = head < q_heads;
+            const uint16_t *h = row + (is_q ? head * 128 : k_offset + (head - q_heads) * 128);
+            const float *scale = is_q ? q_scale : k_scale;
+            float v[128], lane[32], next[32], x[128];
+            for (int c = 0; c < 128; c++) v[c] = f16_to_f32(h[c]);
+            for (int l = 0; l < 32; l++) {
+                float s0 = v[4 * l] * v[4 * l], s1 = v[4 * l + 1] * v[4 * l + 1];
+                float s2 = v[4 * l + 2] * v[4 * l + 2], s3 = v[4 * l + 3] * v[4 * l + 3];
+                lane[l] = (s0 + s1) + (s2 + s3);
+            }
+            for (int off = 16; off >= 1; off >>= 1) {
+                for (int l = 0; l < 32; l++) next[l] = lane[l] + lane[l ^ off];
+                memcpy(lane, next, sizeof lane);
+            }
+            float mean = lane[0] * 0.0078125f;
+            float rinv = 1.0f / sqrtf(mean + eps);
+            for (int c = 0; c < 128; c++) {
+                float normed = v[c] * rinv;
+                x[c] = bf(normed * (scale[c] + 1.0f));
+            }
+            uint16_t *dst = is_q ? q_out + t * q_heads * 128 + head * 128 : k_out + t * kv_heads * 128 + (head - q_heads) * 128;
+            for (int c = 0; c < 128; c++) {
+                float rot = (c % 2 == 0) ? (0.0f - x[c + 1]) : x[c - 1];
+                float xc = x[c] * cos_table[t * 128 + c];
+                float rs = rot * sin_table[t * 128 + c];
+                dst[c] = f32_to_f16(bf(xc + rs));
+            }
+        }
+    }
+}
+
+/* kernels/native/v_transpose.loom: x [rows][width] -> out [width][capacity]; inside the last 32-row
+ * tile the columns past `rows` are written as zero, everything further right is left alone. */
+void oracle_v_transpose(size_t rows, const uint16_t *x, uint16_t *out, size_t width, size_t capacity) {
+    size_t padded = (rows + 31) / 32 * 32;
+    if (padded > capacity) padded = capacity;
+    for (size_t c = 0; c < width; c++)
+        for (size_t r = 0; r < padded; r++) out[c * capacity + r] = r < rows ? x[r * width + c] : 0;
+}
+
+/* Grouped-query attention in f64 (the CPU softmax the reference's own test compares with,
+ * tests/quantized.rs:314-338): a tolerance reference, not a bit reference. */
+void oracle_attention_gqa(size_t queries, size_t tokens, size_t q_heads, size_t kv_heads, const uint16_t *q,
+                          const uint16_t *k, const uint16_t *v, double *out, double scale) {
+    size_t group = q_heads / kv_heads;
+#pragma omp parallel for schedule(dynamic) collapse(2)
+    for (ptrdiff_t t = 0; t < (ptrdiff_t)queries; t++)
+        for (ptrdiff_t head = 0; head < (ptrdiff_t)q_heads; head++) {
+            size_t kvh = (size_t)head / group;
+            double *scores = (double *)malloc(tokens * sizeof(double));
+            double qv[128], mx = -INFINITY, sum = 0.0, acc[128];
+            for (int c = 0; c < 128; c++) qv[c] = f16_to_f32(q[((size_t)t * q_heads + head) * 128 + c]), acc[c] = 0.0;
+            for (size_t j = 0; j < tokens; j++) {
+                double s = 0.0;
+                for (int c = 0; c < 128; c++) s += qv[c] * f16_to_f32(k[(j * kv_heads + kvh) * 128 + c]);
+                scores[j] = s * scale;
+                if (scores[j] > mx) mx = scores[j];
+            }
+            for (size_t j = 0; j < tokens; j++) {
+                double w = exp(scores[j] - mx);
+                sum += w;
+                for (int c = 0; c < 128; c++) acc[c] += w * f16_to_f32(v[(j * kv_heads + kvh) * 128 + c]);
+            }
+            for (int c = 0; c < 128; c++) out[((size_t)t * q_heads + head) * 128 + c] = acc[c] / sum;
+            free(scores);
+        }
+}
