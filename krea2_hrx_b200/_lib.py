@@ -120,6 +120,7 @@ SIGNATURES = {
     "krea2_session_tokens": (c_size_t, [c_void_p]),
     "krea2_session_layers": (c_size_t, [c_void_p]),
     "krea2_session_set_profile": (c_int, [c_void_p, c_int]),
+    "krea2_session_set_attention": (c_int, [c_void_p, c_int]),
     "krea2_session_stage_profile": (c_size_t, [c_void_p, POINTER(c_char_p), POINTER(c_double), c_size_t]),
     "krea2_session_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t]),
     "krea2_session_run_device": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p,

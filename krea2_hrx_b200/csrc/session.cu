@@ -3,12 +3,12 @@
 // fixed scratch buffers sized by shape::capacity, the per-block launch chain, and a CUDA graph
 // of the whole chain that every device-side forward replays.
 //
-// The W8A8 stages -- prepare_norm, qkv|gate GEMM, prepare_gated, wo GEMM + residual,
-// prepare_norm, gate|up GEMM + SwiGLU, prepare_plain, down GEMM + residual -- are the
-// reference's (src/session/mod.rs:671-840).  The three launches between the qkv|gate GEMM
-// and the gated prologue (QK-norm + RoPE, V transpose, fp16 attention) are not part of the
-// W8A8 path; their slot is filled by a stand-in that copies the query columns of the fused
-// buffer into the attention output, so that the chain has data of the right shape and dtype.
+// A block is the reference's eleven launches (src/session/mod.rs:671-840): prepare_norm, qkv|gate
+// GEMM, QK-norm + RoPE, V transpose, fp16 attention, prepare_gated, wo GEMM + residual,
+// prepare_norm, gate|up GEMM + SwiGLU, prepare_plain, down GEMM + residual.  With attention
+// switched off (krea2_session_set_attention) the three launches that are not W8A8 products are
+// replaced by a copy of the query columns of the fused buffer into the attention output: the
+// W8A8 chain alone, which the CPU oracle reproduces bit for bit.
 #include <atomic>
 #include <cstdlib>
 #include <map>
@@ -144,10 +144,13 @@ struct krea2_session {
     size_t qkvg = 0, gate_offset = 0;
     // src/session/mod.rs:76-93
     uint8_t *x = nullptr, *a_q = nullptr, *fused = nullptr, *attn_gu = nullptr;
+    uint8_t *q = nullptr, *k = nullptr, *v = nullptr, *v_transposed = nullptr;
     float *a_s = nullptr, *mods = nullptr, *cos = nullptr, *sin = nullptr;
     size_t x_bytes = 0, a_q_bytes = 0, fused_bytes = 0, attn_gu_bytes = 0, mods_bytes = 0, rope_bytes = 0;
+    size_t q_bytes = 0, kv_bytes = 0;
     cudaGraphExec_t graph = nullptr;
     bool profile = false, poisoned = false;
+    bool attention = true;  // false: the W8A8 chain alone, a copy of the query columns in attention's place
     bool rope_valid = false;
     uint64_t rope_print[2] = {0, 0};
     std::vector<Stage> stages;
@@ -169,7 +172,7 @@ uint64_t fingerprint(const float *values, size_t count) {
 
 struct BlockPointers {
     const int8_t *qkvg_q, *wo_q, *gu_q, *down_q;
-    const float *qkvg_s, *wo_s, *gu_s, *down_s, *prenorm, *postnorm;
+    const float *qkvg_s, *wo_s, *gu_s, *down_s, *prenorm, *postnorm, *qnorm, *knorm;
 };
 
 int locate(const krea2_weights *w, const std::string &name, size_t expect_bytes, const void **out) {
@@ -200,56 +203,71 @@ int block_pointers(const krea2_session *s, size_t index, BlockPointers *b) {
     KREA2_AT(down_s, const float *, ".down.s", d.hidden * 4)
     KREA2_AT(prenorm, const float *, ".prenorm", d.hidden * 4)
     KREA2_AT(postnorm, const float *, ".postnorm", d.hidden * 4)
+    KREA2_AT(qnorm, const float *, ".qnorm", d.head_dim * 4)
+    KREA2_AT(knorm, const float *, ".knorm", d.head_dim * 4)
 #undef KREA2_AT
     return KREA2_OK;
 }
 
-constexpr int kStagesPerBlock = 9;
-const char *const kStageLabels[kStagesPerBlock] = {
-    "prepare",          "gemm qkvg",        "attention stand-in", "prepare gated", "gemm wo + residual",
-    "prepare",          "gemm gate|up + swiglu", "prepare swiglu",  "gemm down + residual"};
+// At most eleven launches per block (src/session/mod.rs:671-840); a profiled forward brackets
+// each with an event and sums device time per label.
+constexpr int kMaxStagesPerBlock = 11;
 
-// One block's launches in the reference's order (src/session/mod.rs:671-840).  `events`, when
-// given, receives kStagesPerBlock + 1 recorded events bracketing the stages.
-int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *events) {
+// One block's launches in the reference's order.  `events`, when given, receives one event before
+// every stage and one after the last; `labels`, when given, the stage labels in launch order.
+int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *events,
+              std::vector<const char *> *labels = nullptr) {
     BlockPointers w{};
     if (int status = block_pointers(s, index, &w)) return status;
     const krea2_dims &d = s->dims;
     const size_t t = s->tokens, hidden = d.hidden, inter = d.inter;
     const size_t ph = pitch_of(hidden), pi = pitch_of(inter);
     const size_t group = krea2_shape_gemm_m_group();
+    const size_t q_heads = hidden / d.head_dim, kv_width = d.kv_heads * d.head_dim;
     const float *mods = s->mods + index * 6 * hidden;  // prescale, preshift, pregate, postscale, postshift, postgate
     int stage = 0;
-    auto mark = [&]() -> int {
+    auto mark = [&](const char *label) -> int {
         if (events) KREA2_CUDA(cudaEventRecord(events[stage], stream));
+        if (labels && label) labels->push_back(label);
         stage++;
         return KREA2_OK;
     };
     int status = KREA2_OK;
-#define KREA2_STEP(call)                    \
-    if ((status = mark())) return status;   \
+#define KREA2_STEP(label, call)                  \
+    if ((status = mark(label))) return status;   \
     if ((status = (call))) return status;
-    KREA2_STEP(krea2_prepare_norm_i8(stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph, 1e-5f))
-    KREA2_STEP(krea2_gemm_i8_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
-    {
-        if ((status = mark())) return status;
+    KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph,
+                                                1e-5f))
+    KREA2_STEP("gemm qkvg",
+               krea2_gemm_i8_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
+    if (s->attention) {
+        // src/session/mod.rs:714-755: QK norm + RoPE out of the fused buffer, V transposed, fp16 attention
+        KREA2_STEP("qk norm + rope",
+                   krea2_rope_qknorm_f16(stream, t, s->fused, w.qnorm, w.knorm, s->cos, s->sin, s->q, s->k, s->v, s->qkvg,
+                                         q_heads, d.kv_heads, hidden, 1e-5f))
+        KREA2_STEP("V transpose", krea2_v_transpose(stream, t, s->v, s->v_transposed, kv_width, s->capacity))
+        KREA2_STEP("f16 attention",
+                   krea2_attention_gqa_lds_f16_wmma(stream, t, d.kv_heads, s->q, s->k, s->v_transposed, s->attn_gu, hidden,
+                                                    kv_width, hidden, s->capacity, 0.08838834764831845f))
+    } else {
+        if ((status = mark("attention stand-in"))) return status;
         KREA2_CUDA(cudaMemcpy2DAsync(s->attn_gu, hidden * 2, s->fused, s->qkvg * 2, hidden * 2, t,
                                      cudaMemcpyDeviceToDevice, stream));
     }
-    KREA2_STEP(krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q, s->a_s, hidden, ph,
-                                      s->qkvg))
-    KREA2_STEP(krea2_gemm_i8_resid_256(stream, t, s->a_q, w.wo_q, w.wo_s, s->a_s, s->x, mods + 2 * hidden, hidden, ph,
-                                       hidden, group))
-    KREA2_STEP(krea2_prepare_norm_i8(stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q, s->a_s,
-                                     hidden, ph, 1e-5f))
-    KREA2_STEP(krea2_gemm_i8_swiglu_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu, hidden, ph, 2 * inter,
-                                        group))
-    KREA2_STEP(krea2_prepare_plain_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
-    KREA2_STEP(krea2_gemm_i8_resid_256x256(stream, t, s->a_q, w.down_q, w.down_s, s->a_s, s->x, mods + 5 * hidden,
-                                           inter, pi, hidden, group,
-                                           static_cast<size_t>(krea2_shape_gemm_schedule_rows(t))))
+    KREA2_STEP("prepare gated", krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q, s->a_s,
+                                                       hidden, ph, s->qkvg))
+    KREA2_STEP("gemm wo + residual", krea2_gemm_i8_resid_256(stream, t, s->a_q, w.wo_q, w.wo_s, s->a_s, s->x,
+                                                             mods + 2 * hidden, hidden, ph, hidden, group))
+    KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q,
+                                                s->a_s, hidden, ph, 1e-5f))
+    KREA2_STEP("gemm gate|up + swiglu", krea2_gemm_i8_swiglu_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu, hidden,
+                                                                 ph, 2 * inter, group))
+    KREA2_STEP("prepare swiglu", krea2_prepare_plain_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
+    KREA2_STEP("gemm down + residual",
+               krea2_gemm_i8_resid_256x256(stream, t, s->a_q, w.down_q, w.down_s, s->a_s, s->x, mods + 5 * hidden, inter, pi,
+                                           hidden, group, static_cast<size_t>(krea2_shape_gemm_schedule_rows(t))))
 #undef KREA2_STEP
-    if ((status = mark())) return status;
+    if ((status = mark(nullptr))) return status;
     return KREA2_OK;
 }
 
@@ -294,24 +312,27 @@ int record_graph(krea2_session *s) {
 // Every block eagerly with an event between stages; the stage table adds up device time per
 // label (src/session/mod.rs:627-647 reports the same sums from a profiled replay).
 int run_profiled(krea2_session *s, size_t first, size_t count) {
-    const size_t per = kStagesPerBlock + 1;
+    const size_t per = kMaxStagesPerBlock + 1;
     if (s->events.size() < count * per) {
         size_t old = s->events.size();
         s->events.resize(count * per);
         for (size_t i = old; i < s->events.size(); i++) KREA2_CUDA(cudaEventCreate(&s->events[i]));
     }
-    for (size_t i = 0; i < count; i++)
-        if (int status = run_block(s, s->stream, first + i, s->events.data() + i * per)) return status;
+    std::vector<const char *> labels;
+    for (size_t i = 0; i < count; i++) {
+        labels.clear();
+        if (int status = run_block(s, s->stream, first + i, s->events.data() + i * per, &labels)) return status;
+    }
     KREA2_CUDA(cudaStreamSynchronize(s->stream));
     s->stages.clear();
     for (size_t i = 0; i < count; i++)
-        for (int k = 0; k < kStagesPerBlock; k++) {
+        for (size_t k = 0; k < labels.size(); k++) {
             float ms = 0.0f;
             KREA2_CUDA(cudaEventElapsedTime(&ms, s->events[i * per + k], s->events[i * per + k + 1]));
             bool found = false;
             for (auto &stage : s->stages)
-                if (std::string(stage.label) == kStageLabels[k]) stage.millis += ms, found = true;
-            if (!found) s->stages.push_back(Stage{kStageLabels[k], ms});
+                if (std::string(stage.label) == labels[k]) stage.millis += ms, found = true;
+            if (!found) s->stages.push_back(Stage{labels[k], ms});
         }
     return KREA2_OK;
 }
@@ -436,6 +457,7 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     KREA2_REQUIRE(weights && out, "session_create: null argument");
     KREA2_REQUIRE(layers <= weights->layers, "the weights hold %zu blocks, %zu were asked for", weights->layers, layers);
     if (int status = prepare_gemm_device()) return status;
+    if (int status = prepare_attention_device()) return status;
     std::unique_ptr<krea2_session> s(new krea2_session);
     s->stream = static_cast<cudaStream_t>(stream);
     s->tokens = tokens, s->layers = layers, s->capacity = krea2_shape_capacity(tokens);
@@ -448,6 +470,10 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     s->attn_gu_bytes = cap * (inter > hidden ? inter : hidden) * 2;
     s->mods_bytes = layers * 6 * hidden * 4;
     s->rope_bytes = cap * s->dims.head_dim * 4;
+    s->q_bytes = cap * hidden * 2;
+    s->kv_bytes = cap * s->dims.kv_heads * s->dims.head_dim * 2;
+    // The attention kernel is built for 128 channels per head; other shapes keep the W8A8 chain only.
+    s->attention = s->dims.head_dim == 128 && hidden % 128 == 0 && (hidden / 128) % s->dims.kv_heads == 0;
     auto destroy = [](krea2_session *p) { krea2_session_destroy(p); };
     std::unique_ptr<krea2_session, decltype(destroy)> guard(s.release(), destroy);
     krea2_session *p = guard.get();
@@ -459,6 +485,16 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->mods), p->mods_bytes));
     KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->cos), p->rope_bytes));
     KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->sin), p->rope_bytes));
+    KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->q), p->q_bytes));
+    KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->k), p->kv_bytes));
+    KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->v), p->kv_bytes));
+    KREA2_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->v_transposed), p->kv_bytes));
+    KREA2_CUDA(cudaMemsetAsync(p->q, 0, p->q_bytes, p->stream));
+    KREA2_CUDA(cudaMemsetAsync(p->k, 0, p->kv_bytes, p->stream));
+    KREA2_CUDA(cudaMemsetAsync(p->v, 0, p->kv_bytes, p->stream));
+    KREA2_CUDA(cudaMemsetAsync(p->v_transposed, 0, p->kv_bytes, p->stream));  // the headroom columns stay zero
+    KREA2_CUDA(cudaMemsetAsync(p->cos, 0, p->rope_bytes, p->stream));
+    KREA2_CUDA(cudaMemsetAsync(p->sin, 0, p->rope_bytes, p->stream));
     // Headroom rows are read and must be zero (src/session/mod.rs:336-340).
     KREA2_CUDA(cudaMemsetAsync(p->x, 0, p->x_bytes, p->stream));
     KREA2_CUDA(cudaMemsetAsync(p->fused, 0, p->fused_bytes, p->stream));
@@ -476,7 +512,7 @@ extern "C" void krea2_session_destroy(krea2_session *s) {
     if (!s) return;
     if (s->graph) cudaGraphExecDestroy(s->graph);
     for (cudaEvent_t e : s->events) cudaEventDestroy(e);
-    void *buffers[] = {s->x, s->a_q, s->a_s, s->fused, s->attn_gu, s->mods, s->cos, s->sin};
+    void *buffers[] = {s->x, s->a_q, s->a_s, s->fused, s->attn_gu, s->mods, s->cos, s->sin, s->q, s->k, s->v, s->v_transposed};
     for (void *b : buffers)
         if (b) cudaFree(b);
     krea2_weights_release(s->weights);
@@ -502,7 +538,23 @@ extern "C" size_t krea2_session_stage_profile(const krea2_session *s, const char
     return n;
 }
 extern "C" size_t krea2_session_launches_per_forward(const krea2_session *s) {
-    return s ? s->layers * (kStagesPerBlock - 1) : 0;  // the stand-in copy is not a kernel of this library
+    // eleven kernels per block with attention; eight without (the stand-in copy is not a kernel of this library)
+    return s ? s->layers * (s->attention ? 11 : 8) : 0;
+}
+
+extern "C" int krea2_session_set_attention(krea2_session *s, int enable) {
+    if (!s) return 0;
+    const int previous = s->attention ? 1 : 0;
+    const bool possible = s->dims.head_dim == 128 && s->dims.hidden % 128 == 0 && (s->dims.hidden / 128) % s->dims.kv_heads == 0;
+    const bool next = enable != 0 && possible;
+    if (next != s->attention) {
+        s->attention = next;
+        if (s->graph) {  // the recording holds the other launch list
+            cudaGraphExecDestroy(s->graph);
+            s->graph = nullptr;
+        }
+    }
+    return previous;
 }
 
 extern "C" int krea2_session_run(krea2_session *s, krea2_stream stream, uint16_t *host_x, const float *host_mods,
@@ -570,6 +622,10 @@ extern "C" int krea2_session_buffer(const krea2_session *s, const char *name, vo
     else if (n == "fused") *ptr = s->fused, *bytes = s->fused_bytes;
     else if (n == "attn_gu") *ptr = s->attn_gu, *bytes = s->attn_gu_bytes;
     else if (n == "mods") *ptr = s->mods, *bytes = s->mods_bytes;
+    else if (n == "q") *ptr = s->q, *bytes = s->q_bytes;
+    else if (n == "k") *ptr = s->k, *bytes = s->kv_bytes;
+    else if (n == "v") *ptr = s->v, *bytes = s->kv_bytes;
+    else if (n == "v_transposed") *ptr = s->v_transposed, *bytes = s->kv_bytes;
     else return fail(KREA2_INVALID_ARGUMENT, "no session buffer named %s", name);
     return KREA2_OK;
 }

@@ -111,6 +111,10 @@ class Session:
     def set_profile(self, enable: bool) -> bool:
         return bool(lib().krea2_session_set_profile(self._handle, int(enable)))
 
+    def set_attention(self, enable: bool) -> bool:
+        """Full block (True) or the W8A8 chain with a copy in attention's place (False)."""
+        return bool(lib().krea2_session_set_attention(self._handle, int(enable)))
+
     def stage_profile(self) -> List[Tuple[str, float]]:
         labels = (ctypes.c_char_p * 16)()
         millis = (ctypes.c_double * 16)()

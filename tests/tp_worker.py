@@ -44,6 +44,7 @@ def main():
     x_dev = torch.from_numpy(x.copy()).view(torch.bfloat16).cuda()
     mods_dev = torch.from_numpy(mods).cuda()
     single = session.Session(stream, weights, tokens, layers)
+    single.set_attention(False)  # the sharded chain is the W8A8 chain
     fabric = parallel.SymmetricFabric()
     tp = parallel.TensorParallel(fabric, rank, dims, parallel.shard_weights(weights, layers, world, rank), tokens)
     fabric.barrier()
