@@ -3,9 +3,11 @@
 
 A "step" is the W8A8 chain of the 28 transformer blocks for one 1024x1024 image (4096 image +
 512 text tokens) at the reference's dimensions (d 6144, q|k|v|gate 15360, SwiGLU 16384): per
-block prepare_norm -> gemm qkvg -> [attention stand-in: a copy] -> prepare_gated -> gemm wo +
+block prepare_norm -> gemm qkvg -> [a copy in attention's place] -> prepare_gated -> gemm wo +
 residual -> prepare_norm -> gemm gate|up + SwiGLU -> prepare_plain -> gemm down + residual, on
 seeded synthetic int8 weights (12.2 GB, so every step streams far more than L2 holds).
+`full_block_step` in the output is the same step with the session's attention on (QK-norm +
+RoPE, V transpose, fp16 attention: the reference's eleven launches per block).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
@@ -202,6 +204,7 @@ def run_b200(args, dims, config):
     weights = session.Weights(mdims, layers)
     weights.fill_synthetic(1234, stream)  # replicated: the same seed on every rank
     s = session.Session(stream, weights, tokens, layers)
+    s.set_attention(False)  # the headline is the W8A8 chain; the full block is measured further down
     # consecutive seeds per image, as `--images N` does (src/main.rs:48-50)
     gen = torch.Generator().manual_seed(rank)
     x_host = torch.randn((tokens, mdims.hidden), generator=gen).to(torch.bfloat16).pin_memory()
@@ -255,6 +258,37 @@ def run_b200(args, dims, config):
     s.run(stream, x_prof, mods_host, cos, sin)
     stage_ms = dict(s.stage_profile())
     s.set_profile(False)
+
+    # The full block chain (QK-norm + RoPE, V transpose and fp16 attention between the q|k|v|gate GEMM and
+    # the gated prologue): what one denoising step of the 28 blocks costs, beside the W8A8 chain above.
+    full = None
+    s.set_attention(True)
+    if s.set_attention(True):  # the second call reports whether the first one took (head shape permitting)
+        for _ in range(2):
+            device_step()
+        barrier()
+        f_start, f_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f_start.record(stream)
+        for _ in range(args.steps):
+            device_step()
+        f_end.record(stream)
+        barrier()
+        full_ms = torch.tensor([f_start.elapsed_time(f_end) / args.steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(full_ms, op=dist.ReduceOp.MAX)
+        s.set_profile(True)
+        s.run(stream, x_prof, mods_host, cos, sin)
+        full_stage_ms = dict(s.stage_profile())
+        s.set_profile(False)
+        q_heads = mdims.hidden // mdims.head_dim
+        attention_flop = 4.0 * tokens * tokens * mdims.head_dim * q_heads
+        attention_ms = full_stage_ms.get("f16 attention", 0.0) / layers
+        full = {"ms_per_step": full_ms.item(), "launches_per_step": s.launches_per_forward(),
+                "attention_ms_per_launch": attention_ms,
+                "attention_tflops": attention_flop / (attention_ms * 1e-3) / 1e12 if attention_ms else None,
+                "rope_ms_per_launch": full_stage_ms.get("qk norm + rope", 0.0) / layers,
+                "v_transpose_ms_per_launch": full_stage_ms.get("V transpose", 0.0) / layers}
+    s.set_attention(False)
     status = k.device_status()
 
     if rank == 0:
@@ -293,6 +327,7 @@ def run_b200(args, dims, config):
             "roofline": roofline,
             "kernels": kernels,
             "frac_of_nominal_int8_peak": value / world / NOMINAL_INT8_TOPS,
+            "full_block_step": full,
             "device_status": status,
         }
         if world == 1 and not args.no_cpu_baseline:

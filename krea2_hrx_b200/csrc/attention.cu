@@ -11,12 +11,13 @@
 // Attention is a flash-attention forward on the fifth-generation tensor cores: one CTA per
 // (128 query rows, query head); S = Q K^T and O += P V are tcgen05.mma kind::f16 with f32
 // accumulators in tensor memory, K and V^T tiles of 128 keys arrive by TMA (128-byte swizzle,
-// two stages each), four softmax warps read S from tensor memory (one query row per thread),
+// two stages each), softmax warps read S from tensor memory (one query row per thread),
 // keep the running maximum and sum in registers and hand P to the second product through shared
 // memory.  O stays in tensor memory across key tiles; it is rescaled there only when a row's
 // maximum moves by more than 2^8 (the reference maximum used for the exponentials is otherwise
-// left stale, which changes neither O nor the sum's ratio).  S is double-buffered so that the
-// next tile's Q K^T runs under the current tile's softmax.
+// left stale, which changes neither O nor the sum's ratio).  Two softmax groups of four warps take
+// alternate key tiles, each with its own S buffer, P tile, O accumulator, maximum and sum, so that
+// one group's exponentials run while the other waits for scores; the halves are merged at the end.
 #include <cuda.h>
 
 #include <mutex>
@@ -102,10 +103,11 @@ v_transpose_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out, u
 constexpr int kTile = 128;            // query rows per CTA, keys per step, channels per head
 constexpr int kSubtileBytes = 16384;  // [128 rows][64 f16]: one 128-byte swizzled column block
 constexpr int kOperandBytes = 2 * kSubtileBytes;
-constexpr int kAttnThreads = 192;     // warps 0-3 softmax, 4 TMA, 5 MMA
-constexpr int kSoftmaxWarps = 4;
+constexpr int kAttnThreads = 320;     // warps 0-3 and 4-7: two softmax groups; 8 TMA; 9 MMA
+constexpr int kGroupWarps = 4;
+constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9;
 constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
-constexpr int kAttnSmemBytes = 6 * kOperandBytes + 1024 + 256;  // Q, K x2, V x2, P
+constexpr int kAttnSmemBytes = 7 * kOperandBytes + 1024 + 256 + 1024;  // Q, K x2, V x2, P x2, barriers, merge
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint64_t timer_ns() {
@@ -175,7 +177,9 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_load_32(uint32_t address, float (&r)[32]) {
+__device__ __forceinline__ void tmem_wait_load() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Issues the load of 32 columns without waiting for it (tmem_wait_load completes all loads issued so far).
+__device__ __forceinline__ void tmem_load_32_async(uint32_t address, float *r) {
     uint32_t *u = reinterpret_cast<uint32_t *>(r);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -186,7 +190,10 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, float (&r)[32]) {
           "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
           "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
         : "r"(address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t address, float (&r)[32]) {
+    tmem_load_32_async(address, r);
+    tmem_wait_load();
 }
 __device__ __forceinline__ void tmem_store_32(uint32_t address, const float (&r)[32]) {
     const uint32_t *u = reinterpret_cast<const uint32_t *>(r);
@@ -239,12 +246,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_smem = smem, *k_smem = smem + kOperandBytes, *v_smem = smem + 3 * kOperandBytes;
-    uint8_t *p_smem = smem + 5 * kOperandBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 6 * kOperandBytes);
+    uint8_t *p_smem = smem + 5 * kOperandBytes;  // one P tile per softmax group
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 7 * kOperandBytes);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
-    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *p_empty = bars + 14, *o_done = bars + 15;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *p_empty = bars + 15, *o_done = bars + 17;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *merge = reinterpret_cast<float *>(smem + 7 * kOperandBytes + 256);  // group 1's (reference, sum) per row
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q0 = blockIdx.x * kTile, head = blockIdx.y, kv_head = head / g.q_heads_per_kv;
@@ -258,16 +266,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             mbar_init(v_full + s, 1);
             mbar_init(v_empty + s, 1);
             mbar_init(s_full + s, 1);
-            mbar_init(s_empty + s, kSoftmaxWarps);
+            mbar_init(s_empty + s, kGroupWarps);
+            mbar_init(p_full + s, kGroupWarps);
+            mbar_init(p_empty + s, 1);
         }
-        mbar_init(p_full, kSoftmaxWarps);
-        mbar_init(p_empty, 1);
         mbar_init(o_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kMmaWarpAttn) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
                      : "memory");
@@ -276,10 +284,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 2 * kTile;  // S buffers at columns 0 and 128, O at 256
+    const uint32_t tmem_base = *tmem_slot;  // S of group 0 and 1 at columns 0 and 128, their O at 256 and 384
 
-    if (warp == 4) {
+    if (warp == kTmaWarpAttn) {
         if (lane == 0) {
             mbar_expect_tx(q_full, kOperandBytes);
             tma_load_2d(q_smem, &map_q, q_full, static_cast<int>(head * kTile), static_cast<int>(q0));
@@ -304,13 +311,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarpAttn) {
         if (lane == 0) {
             bool alive = mbar_wait(q_full, 0, abort_flag);
             tc_fence_after();
-            const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+            const uint32_t q_addr = smem_u32(q_smem);
+            // Key tile j belongs to softmax group j & 1, which owns S buffer, P tile and O accumulator j & 1.
             for (uint32_t j = 0; alive && j <= tiles; j++) {
-                if (j < tiles) {  // S_j = Q K_j^T into S buffer j & 1
+                if (j < tiles) {  // S_j = Q K_j^T
                     const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
                     if (!mbar_wait(k_full + s, phase, abort_flag) || !mbar_wait(s_empty + s, phase ^ 1u, abort_flag)) break;
                     tc_fence_after();
@@ -318,55 +326,68 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     umma_commit(s_full + s);
                     umma_commit(k_empty + s);
                 }
-                if (j > 0) {  // O += P_{j-1} V_{j-1}
+                if (j > 0) {  // O_group += P_{j-1} V_{j-1}
                     const uint32_t i = j - 1, s = i & 1u, phase = (i >> 1) & 1u;
-                    if (!mbar_wait(p_full, i & 1u, abort_flag) || !mbar_wait(v_full + s, phase, abort_flag)) break;
+                    if (!mbar_wait(p_full + s, phase, abort_flag) || !mbar_wait(v_full + s, phase, abort_flag)) break;
                     tc_fence_after();
-                    issue_product(tmem_o, p_addr, smem_u32(v_smem + s * kOperandBytes), i > 0);
-                    umma_commit(p_empty);
+                    issue_product(tmem_base + (2 + s) * kTile, smem_u32(p_smem + s * kOperandBytes),
+                                  smem_u32(v_smem + s * kOperandBytes), i >= 2);
+                    umma_commit(p_empty + s);
                     umma_commit(v_empty + s);
                     if (j == tiles) umma_commit(o_done);
                 }
             }
         }
     } else {
-        // Softmax warps: warp w owns TMEM lanes 32w..32w+31 = query rows q0 + 32w + lane.
-        const uint32_t lane_bits = static_cast<uint32_t>(warp * 32) << 16;
-        const uint32_t row_in_tile = warp * 32 + lane;
+        // Two softmax groups of four warps.  Group `grp` takes key tiles grp, grp + 2, ... and runs its own
+        // online softmax over them (own reference maximum, sum, P tile and O accumulator); the two partial
+        // results are merged at the end.  While one group waits for its scores or reduces a maximum the
+        // other keeps the exponential unit busy.  Warp w reads TMEM lanes 32 * (w % 4) .. + 31.
+        const int grp = warp >> 2, quarter = warp & 3;
+        const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t row_in_tile = quarter * 32 + lane;
+        const uint32_t s_addr = tmem_base + grp * kTile + lane_bits, o_addr = tmem_base + (2 + grp) * kTile + lane_bits;
+        uint8_t *p_tile = p_smem + grp * kOperandBytes;
         float reference = -INFINITY, sum = 0.0f;  // in units of log2: scores are scaled by scale * log2(e)
         bool alive = true;
-        for (uint32_t j = 0; j < tiles; j++) {
-            const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
-            const bool ready = mbar_wait(s_full + s, phase, abort_flag);
+        for (uint32_t j = grp; j < tiles; j += 2) {
+            const uint32_t turn = j >> 1;
+            const bool ready = mbar_wait(s_full + grp, turn & 1u, abort_flag);
             if (!__all_sync(kFull, ready)) {
                 alive = false;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = tmem_base + s * kTile + lane_bits;
             const uint32_t valid = g.tokens - j * kTile;  // keys of this tile before the end of the sequence
-            // pass 1: the row's maximum over this tile's valid keys
-            float tile_max = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                float v[32];
-                tmem_load_32(s_addr + c * 32, v);
+            // The whole row of S (128 scores) comes into registers with four loads in flight at once.
+            float v[kTile];
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    if (static_cast<uint32_t>(c * 32 + i) < valid) tile_max = fmaxf(tile_max, v[i]);
+            for (int c = 0; c < 4; c++) tmem_load_32_async(s_addr + c * 32, v + c * 32);
+            tmem_wait_load();
+            if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
+#pragma unroll
+                for (int i = 0; i < kTile; i++)
+                    if (static_cast<uint32_t>(i) >= valid) v[i] = -INFINITY;
             }
+            float part[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) part[i] = v[i];
+#pragma unroll
+            for (int i = 8; i < kTile; i++) part[i & 7] = fmaxf(part[i & 7], v[i]);
+            float tile_max = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
+                                   fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
             tile_max *= g.scale_log2;
             // The exponent reference moves only when the maximum has grown by more than 2^8.
             float alpha = 1.0f;
             const bool move = tile_max > reference + 8.0f;
             if (move) {
-                alpha = fast_exp2(reference - tile_max);  // 0 on the first tile
+                alpha = fast_exp2(reference - tile_max);  // 0 on the group's first tile
                 reference = tile_max;
                 sum *= alpha;
             }
-            // P and O of the previous tile must be consumed before P is overwritten and O rescaled.
-            if (j > 0) {
-                const bool consumed = mbar_wait(p_empty, (j - 1) & 1u, abort_flag);
+            // The group's previous P and O must be consumed before P is overwritten and O rescaled.
+            if (turn > 0) {
+                const bool consumed = mbar_wait(p_empty + grp, (turn - 1) & 1u, abort_flag);
                 if (!__all_sync(kFull, consumed)) {
                     alive = false;
                     break;
@@ -376,29 +397,28 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll 1
                     for (int c = 0; c < 4; c++) {
                         float o[32];
-                        tmem_load_32(tmem_o + lane_bits + c * 32, o);
+                        tmem_load_32(o_addr + c * 32, o);
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] *= alpha;
-                        tmem_store_32(tmem_o + lane_bits + c * 32, o);
+                        tmem_store_32(o_addr + c * 32, o);
                     }
                 }
             }
-            // pass 2: p = 2^(score - reference), f16, into the K-major swizzled P tile
-#pragma unroll 1
+            // p = 2^(score - reference), f16, into the K-major swizzled P tile
+            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
             for (int c = 0; c < 4; c++) {
-                float v[32];
-                tmem_load_32(s_addr + c * 32, v);
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = static_cast<uint32_t>(c * 32 + i) < valid ? fast_exp2(fmaf(v[i], g.scale_log2, -reference)) : 0.0f;
-                    float p1 = static_cast<uint32_t>(c * 32 + i + 1) < valid ? fast_exp2(fmaf(v[i + 1], g.scale_log2, -reference)) : 0.0f;
-                    sum += p0 + p1;
+                    const float p0 = fast_exp2(fmaf(v[c * 32 + i], g.scale_log2, -reference));
+                    const float p1 = fast_exp2(fmaf(v[c * 32 + i + 1], g.scale_log2, -reference));
+                    partial[(i >> 1) & 3] += p0 + p1;
                     const __half2 h = __floats2half2_rn(p0, p1);
                     packed[i / 2] = *reinterpret_cast<const uint32_t *>(&h);
                 }
                 // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key subtile row
-                uint8_t *row_base = p_smem + (c >> 1) * kSubtileBytes + row_in_tile * 128;
+                uint8_t *row_base = p_tile + (c >> 1) * kSubtileBytes + row_in_tile * 128;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     const int chunk = (c & 1) * 4 + q;
@@ -406,36 +426,54 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
             }
+            sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's async proxy
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(s_empty + s);
-                mbar_arrive(p_full);
+                mbar_arrive(s_empty + grp);
+                mbar_arrive(p_full + grp);
             }
         }
-        if (alive) {
-            const bool finished = mbar_wait(o_done, 0, abort_flag);
-            if (__all_sync(kFull, finished)) {
-                tc_fence_after();
-                const uint32_t row = q0 + row_in_tile;
-                const float inv = 1.0f / sum;
-                uint16_t *dst = g.out + static_cast<size_t>(row) * g.out_stride + head * kTile;
+        // Merge: group 1 publishes its reference and sum per row; group 0 combines both accumulators.
+        const bool finished = alive && mbar_wait(o_done, 0, abort_flag);
+        if (grp == 1) {
+            merge[row_in_tile] = reference;
+            merge[kTile + row_in_tile] = sum;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
+        if (grp == 0 && __all_sync(kFull, finished)) {
+            tc_fence_after();
+            const float ref_b = merge[row_in_tile], sum_b = merge[kTile + row_in_tile];
+            const float top = fmaxf(reference, ref_b);
+            const float wa = fast_exp2(reference - top);
+            const float wb = tiles > 1 ? fast_exp2(ref_b - top) : 0.0f;  // with one tile group 1 never ran
+            const float inv = 1.0f / (sum * wa + sum_b * wb);
+            const float fa = wa * inv, fb = wb * inv;
+            const uint32_t row = q0 + row_in_tile;
+            uint16_t *dst = g.out + static_cast<size_t>(row) * g.out_stride + head * kTile;
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    float o[32];
-                    tmem_load_32(tmem_o + lane_bits + c * 32, o);
-                    if (row < g.tokens) {
+            for (int c = 0; c < 4; c++) {
+                float oa[32], ob[32];
+                tmem_load_32_async(tmem_base + 2 * kTile + lane_bits + c * 32, oa);
+                if (tiles > 1) tmem_load_32_async(tmem_base + 3 * kTile + lane_bits + c * 32, ob);
+                tmem_wait_load();
+                if (row < g.tokens) {
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            uint32_t w[4];
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const __half2 h = __floats2half2_rn(o[8 * q + 2 * i] * inv, o[8 * q + 2 * i + 1] * inv);
-                                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+                        for (int i = 0; i < 4; i++) {
+                            const int e = 8 * q + 2 * i;
+                            float lo = oa[e] * fa, hi = oa[e + 1] * fa;
+                            if (tiles > 1) {
+                                lo = fmaf(ob[e], fb, lo);
+                                hi = fmaf(ob[e + 1], fb, hi);
                             }
-                            *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            const __half2 h = __floats2half2_rn(lo, hi);
+                            w[i] = *reinterpret_cast<const uint32_t *>(&h);
                         }
+                        *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -445,7 +483,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 5) {
+    if (warp == kMmaWarpAttn) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
