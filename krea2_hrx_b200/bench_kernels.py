@@ -129,10 +129,47 @@ def run_prologue(kind, m, dims, iters, warmup, flush):
             "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
 
 
+def run_attention(kind, m, dims, iters, warmup, flush):
+    """The non-W8A8 launches of a block: `rope` (QK-norm + RoPE), `vt` (V transpose), `attention`."""
+    h, qkv = dims["hidden"], dims["qkv"]
+    q_heads = h // 128
+    kv_heads = max(1, (qkv - 2 * h) // 256) if qkv > 2 * h else q_heads  # q|k|v|gate, else q|k|v with equal heads
+    if qkv == 3 * h:
+        kv_heads = q_heads
+    kv_width = kv_heads * 128
+    cap = shape.capacity(m)
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    q = torch.randn((m, h), generator=gen, device="cuda").to(torch.float16)
+    k = torch.randn((m, kv_width), generator=gen, device="cuda").to(torch.float16)
+    v = torch.randn((m, kv_width), generator=gen, device="cuda").to(torch.float16)
+    vt = torch.zeros((kv_width, cap), dtype=torch.float16, device="cuda")
+    out = torch.zeros((m, h), dtype=torch.float16, device="cuda")
+    if kind == "rope":
+        fused = torch.randn((m, qkv), generator=gen, device="cuda").to(torch.float16)
+        scale = [torch.randn(128, generator=gen, device="cuda") * 0.1 for _ in range(2)]
+        cos, sin = torch.rand((m, 128), generator=gen, device="cuda"), torch.rand((m, 128), generator=gen, device="cuda")
+        fn = lambda: ops.rope_qknorm_f16(fused, scale[0], scale[1], cos, sin, q, k, v, qkv, q_heads, kv_heads, h, 1e-5)
+        ms = time_launches(fn, iters, warmup, flush)
+        nbytes = m * (h + 2 * kv_width) * 4
+        return {"kernel": "rope_qknorm_f16", "m": m, "ms": ms, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
+    if kind == "vt":
+        fn = lambda: ops.v_transpose(v, vt, kv_width, cap)
+        ms = time_launches(fn, iters, warmup, flush)
+        nbytes = m * kv_width * 4
+        return {"kernel": "v_transpose", "m": m, "ms": ms, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
+    ops.v_transpose(v, vt, kv_width, cap)
+    fn = lambda: ops.attention_gqa(m, kv_heads, q, k, vt, out, h, kv_width, h, cap, 0.08838834764831845)
+    ms = time_launches(fn, iters, warmup, flush)
+    gflop = 4.0 * m * m * 128 * q_heads / 1e9
+    return {"kernel": "attention_gqa_lds_f16_wmma", "m": m, "q_heads": q_heads, "kv_heads": kv_heads, "ms": ms,
+            "gflop": gflop, "tflops": gflop / ms}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", default="all",
-                        help="qkvg, wo, gu, down, acc, norm, gated, plain, gemms, prologues or all (comma separated)")
+                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, gemms, prologues or all "
+                             "(comma separated)")
     parser.add_argument("--m", default="4608", help="rows, comma separated; 'reference' = the reference's bench list")
     parser.add_argument("--dims", default="reference", choices=sorted(DIMS))
     parser.add_argument("--iters", type=int, default=20)
@@ -147,7 +184,8 @@ def main():
     dims = DIMS[args.dims]
     for kind in kinds:
         for m in rows:
-            runner = run_prologue if kind in ("norm", "gated", "plain") else run_gemm
+            runner = run_prologue if kind in ("norm", "gated", "plain") else \
+                run_attention if kind in ("rope", "vt", "attention") else run_gemm
             result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
             result["dims"] = args.dims
             print(json.dumps(result), flush=True)

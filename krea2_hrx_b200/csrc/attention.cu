@@ -137,6 +137,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
+// One non-blocking look at a barrier phase (the MMA thread polls several barriers in turn).
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
 __device__ int g_attention_status = 0;  // folded into krea2_device_status by take_attention_status
 constexpr int kAttentionTimedOut = 32;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
@@ -316,27 +330,58 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             bool alive = mbar_wait(q_full, 0, abort_flag);
             tc_fence_after();
             const uint32_t q_addr = smem_u32(q_smem);
-            // Key tile j belongs to softmax group j & 1, which owns S buffer, P tile and O accumulator j & 1.
-            for (uint32_t j = 0; alive && j <= tiles; j++) {
-                if (j < tiles) {  // S_j = Q K_j^T
-                    const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
-                    if (!mbar_wait(k_full + s, phase, abort_flag) || !mbar_wait(s_empty + s, phase ^ 1u, abort_flag)) break;
-                    tc_fence_after();
-                    issue_product(tmem_base + s * kTile, q_addr, smem_u32(k_smem + s * kOperandBytes), false);
-                    umma_commit(s_full + s);
-                    umma_commit(k_empty + s);
+            // Key tile j belongs to softmax group j & 1, which owns K/V stage, S buffer, P tile and O
+            // accumulator j & 1, so the two groups' products are independent streams.  The issuing
+            // thread polls both and issues whatever is ready: S of a group's next tile as soon as its S
+            // buffer has been read out, P V of a tile as soon as its P is written.
+            uint32_t s_next[2] = {0u, 1u}, pv_next[2] = {0u, 1u};
+            uint64_t idle_since = 0;
+            uint32_t idle_polls = 0;
+            while (alive) {
+                bool progressed = false, pending = false;
+#pragma unroll
+                for (uint32_t grp = 0; grp < 2; grp++) {
+                    if (s_next[grp] < tiles) {
+                        pending = true;
+                        const uint32_t parity = (s_next[grp] >> 1) & 1u;
+                        if (mbar_test(k_full + grp, parity) && mbar_test(s_empty + grp, parity ^ 1u)) {
+                            tc_fence_after();
+                            issue_product(tmem_base + grp * kTile, q_addr, smem_u32(k_smem + grp * kOperandBytes), false);
+                            umma_commit(s_full + grp);
+                            umma_commit(k_empty + grp);
+                            s_next[grp] += 2;
+                            progressed = true;
+                        }
+                    }
+                    if (pv_next[grp] < tiles) {
+                        pending = true;
+                        const uint32_t turn = pv_next[grp] >> 1, parity = turn & 1u;
+                        if (pv_next[grp] < s_next[grp] && mbar_test(p_full + grp, parity) && mbar_test(v_full + grp, parity)) {
+                            tc_fence_after();
+                            issue_product(tmem_base + (2 + grp) * kTile, smem_u32(p_smem + grp * kOperandBytes),
+                                          smem_u32(v_smem + grp * kOperandBytes), turn > 0);
+                            umma_commit(p_empty + grp);
+                            umma_commit(v_empty + grp);
+                            pv_next[grp] += 2;
+                            progressed = true;
+                        }
+                    }
                 }
-                if (j > 0) {  // O_group += P_{j-1} V_{j-1}
-                    const uint32_t i = j - 1, s = i & 1u, phase = (i >> 1) & 1u;
-                    if (!mbar_wait(p_full + s, phase, abort_flag) || !mbar_wait(v_full + s, phase, abort_flag)) break;
-                    tc_fence_after();
-                    issue_product(tmem_base + (2 + s) * kTile, smem_u32(p_smem + s * kOperandBytes),
-                                  smem_u32(v_smem + s * kOperandBytes), i >= 2);
-                    umma_commit(p_empty + s);
-                    umma_commit(v_empty + s);
-                    if (j == tiles) umma_commit(o_done);
+                if (!pending) break;
+                if (progressed) {
+                    idle_polls = 0;
+                } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up after two seconds without progress
+                    if (idle_polls == 256u) idle_since = timer_ns();
+                    if (*abort_flag) {
+                        alive = false;
+                    } else if (timer_ns() - idle_since > kAttnWaitLimitNs) {
+                        *abort_flag = 1;
+                        atomicOr(&g_attention_status, kAttentionTimedOut);
+                        alive = false;
+                    }
                 }
             }
+            if (alive) umma_commit(o_done);
         }
     } else {
         // Two softmax groups of four warps.  Group `grp` takes key tiles grp, grp + 2, ... and runs its own
@@ -364,6 +409,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_load_32_async(s_addr + c * 32, v + c * 32);
             tmem_wait_load();
+            // The scores are in registers: the S buffer can take the group's next tile already.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + grp);
             if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
 #pragma unroll
                 for (int i = 0; i < kTile; i++)
@@ -430,10 +479,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's async proxy
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_empty + grp);
-                mbar_arrive(p_full + grp);
-            }
+            if (lane == 0) mbar_arrive(p_full + grp);
         }
         // Merge: group 1 publishes its reference and sum per row; group 0 combines both accumulators.
         const bool finished = alive && mbar_wait(o_done, 0, abort_flag);
