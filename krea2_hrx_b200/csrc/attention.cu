@@ -103,9 +103,9 @@ v_transpose_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out, u
 constexpr int kTile = 128;            // query rows per CTA, keys per step, channels per head
 constexpr int kSubtileBytes = 16384;  // [128 rows][64 f16]: one 128-byte swizzled column block
 constexpr int kOperandBytes = 2 * kSubtileBytes;
-constexpr int kAttnThreads = 320;     // warps 0-3 and 4-7: two softmax groups; 8 TMA; 9 MMA
+constexpr int kAttnThreads = 352;     // warps 0-3 and 4-7: two softmax groups; 8 Q+K loads; 9 MMA; 10 V loads
 constexpr int kGroupWarps = 4;
-constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9;
+constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9, kTmaWarpV = 10;
 constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
 constexpr int kAttnSmemBytes = 7 * kOperandBytes + 1024 + 256 + 1024;  // Q, K x2, V x2, P x2, barriers, merge
 
@@ -313,6 +313,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 uint8_t *k_dst = k_smem + s * kOperandBytes;
                 tma_load_2d(k_dst, &map_k, k_full + s, static_cast<int>(kv_head * kTile), key0);
                 tma_load_2d(k_dst + kSubtileBytes, &map_k, k_full + s, static_cast<int>(kv_head * kTile + 64), key0);
+            }
+            if (*abort_flag) {
+                const uint64_t start = timer_ns();
+                while (timer_ns() - start < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == kTmaWarpV) {
+        // V tiles have a producer of their own: a V stage frees up only after its P V product, much
+        // later than the K stage of the same tile, and must not hold back the next K load.
+        if (lane == 0) {
+            for (uint32_t j = 0; j < tiles; j++) {
+                const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+                const int key0 = static_cast<int>(j * kTile);
                 if (!mbar_wait(v_empty + s, phase ^ 1u, abort_flag)) break;
                 mbar_expect_tx(v_full + s, kOperandBytes);
                 uint8_t *v_dst = v_smem + s * kOperandBytes;
