@@ -3,22 +3,44 @@
 //   krea2_prepare_gated_i8  (kernels/prepare_gated_i8.loom)
 //   krea2_prepare_plain_i8  (kernels/prepare_plain_i8.loom)
 //
-// One 256-thread block per token, as the reference lays the row out: thread l owns the
-// 8-element chunks j*256 + l (one 128-bit load each), so warp w holds the aligned
-// 256-element Hadamard group j*8 + w of every step j.  The row lives in registers from
-// the single global read to the packed int8 store; the four radix-4 Hadamard stages run
-// inside the warp (stride 1 in-thread, stride 4 across lane bit 0, strides 16 and 64 by
-// pairs of xor shuffles), and the only block-wide exchanges are the sum of squares and
-// the absmax.  Every f32 step uses the round-to-nearest intrinsics, so the compiler can
-// neither fuse nor reorder them and the bits match the CPU statement of the same order.
+// The kernels are bound by instruction issue, not by HBM, so the layout is chosen to issue few
+// instructions per element:
+//   * one persistent block per SM; inside it several independent row workers (32 threads per
+//     2048 columns each, synchronised by named barriers) so that one worker's loads overlap the
+//     others' arithmetic, and what every row needs is staged in shared memory once per block
+//     (the norm and modulation vectors; the 64 Ki-entry table of bf16(sigmoid(f16)));
+//   * a thread owns 32 positions of each of two 256-element Hadamard groups - the index bits
+//     0-2, 4 and 6 - so each radix-4 stage after the first keeps one of its two digits in the
+//     thread and needs one shuffle per two outputs (1.5 shuffles per element, not 4.5);
+//   * the two groups of a thread travel as the halves of packed f32x2 registers through the
+//     butterflies, the adaLN arithmetic and the scaling (add/sub/mul.rn.f32x2 are the IEEE
+//     operations of their lanes), which halves the arithmetic issue slots.
+// Every f32 step is a single round-to-nearest operation in the order the reference writes, so
+// the bits match the CPU statement; the sum of squares is still taken over the reference's
+// own thread layout (thread l of 256 owns the 8-element chunks j*256 + l).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace krea2 {
 namespace {
 
-constexpr int kThreads = 256;
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kSmemLimit = 232448;       // opt-in dynamic shared memory of one sm_100 block
+constexpr int kWideThreads = 576;        // block size limit of the f32 prologues (112 registers)
+constexpr int kPlainThreads = 768;       // of the f16 prologue, which keeps its row packed
 
+template <int CPL, int MAX_THREADS>
+struct Geometry {
+    static constexpr int kWidth = 2048 * CPL;
+    static constexpr int kChunks = kWidth / 8;          // 16-byte chunks of 8 elements
+    static constexpr int kWorkerThreads = 32 * CPL;     // eight lanes per pair of groups
+    static constexpr int kFit = MAX_THREADS / kWorkerThreads;
+    static constexpr int kWorkers = kFit < 1 ? 1 : (kFit > 15 ? 15 : kFit);
+    static constexpr int kBlockThreads = kWorkers * kWorkerThreads;
+};
+
+// ---------------------------------------------------------------- small pieces
 __device__ __forceinline__ uint4 load_stream(const uint4 *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -27,95 +49,55 @@ __device__ __forceinline__ uint4 load_stream(const uint4 *p) {
     return v;
 }
 
-__device__ __forceinline__ void unpack_bf16(const uint4 &raw, float (&v)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+__device__ __forceinline__ void worker_barrier(int worker, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(worker + 1), "r"(threads) : "memory");
+}
+
+// Two f32 values in one 64-bit register pair: `a` belongs to the first group of the thread,
+// `b` to the second (or, in the adaLN arithmetic, to the next column).
+struct F2 {
+    float a, b;
+};
+
+#define KREA2_PACKED_OP(name, op)                                                                         \
+    __device__ __forceinline__ F2 name(F2 x, F2 y) {                                                      \
+        F2 d;                                                                                             \
+        asm("{ .reg .b64 p, q, r;\n mov.b64 p, {%2, %3};\n mov.b64 q, {%4, %5};\n " op                   \
+            ".rn.f32x2 r, p, q;\n mov.b64 {%0, %1}, r;\n }"                                               \
+            : "=f"(d.a), "=f"(d.b)                                                                        \
+            : "f"(x.a), "f"(x.b), "f"(y.a), "f"(y.b));                                                    \
+        return d;                                                                                         \
     }
+KREA2_PACKED_OP(add2, "add")
+KREA2_PACKED_OP(sub2, "sub")
+KREA2_PACKED_OP(mul2, "mul")
+#undef KREA2_PACKED_OP
+
+__device__ __forceinline__ F2 both(float v) { return F2{v, v}; }
+
+__device__ __forceinline__ F2 shfl2(F2 v, int mask) {
+    return F2{__shfl_xor_sync(kFull, v.a, mask), __shfl_xor_sync(kFull, v.b, mask)};
 }
 
-__device__ __forceinline__ void unpack_f16(const uint4 &raw, float (&v)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
-        v[2 * i] = __low2float(h);
-        v[2 * i + 1] = __high2float(h);
-    }
+// Columns 2k and 2k+1 of a bf16x2 word.
+__device__ __forceinline__ F2 unpack_bf16x2(uint32_t w) {
+    return F2{__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)};
 }
 
-// bf16 rounding of two values with one packed conversion (cvt.rn.bf16x2.f32).
-__device__ __forceinline__ void bf_round2(float &a, float &b) {
-    __nv_bfloat162 packed = __floats2bfloat162_rn(a, b);
-    const uint32_t u = *reinterpret_cast<uint32_t *>(&packed);
-    a = __uint_as_float(u << 16);
-    b = __uint_as_float(u & 0xffff0000u);
+__device__ __forceinline__ F2 unpack_f16x2(uint32_t w) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    return F2{f.x, f.y};
 }
 
-// What each Hadamard stage does to its pair of outputs: nothing for the f32 rotation; a quarter
-// and an f16 rounding for the plain prologue (kernels/prepare_plain_i8.loom:120-127).
-template <bool kHalf>
-__device__ __forceinline__ void stage_round2(float &a, float &b) {
-    if constexpr (kHalf) {
-        const float2 f = __half22float2(__floats2half2_rn(__fmul_rn(a, 0.25f), __fmul_rn(b, 0.25f)));
-        a = f.x;
-        b = f.y;
-    }
+// bf16 rounding of both halves with one packed conversion (cvt.rn.bf16x2.f32).
+__device__ __forceinline__ F2 bf_round2(F2 v) {
+    __nv_bfloat162 packed = __floats2bfloat162_rn(v.a, v.b);
+    return unpack_bf16x2(*reinterpret_cast<uint32_t *>(&packed));
 }
 
-// One radix-4 butterfly (kernels/prepare_norm_i8.loom:194-201).
-template <bool kHalf>
-__device__ __forceinline__ void butterfly(float &e0, float &e1, float &e2, float &e3) {
-    float s01 = __fadd_rn(e0, e1), s23 = __fadd_rn(e2, e3);
-    float d01 = __fsub_rn(e0, e1), d23 = __fsub_rn(e2, e3);
-    e0 = __fadd_rn(s01, d23);
-    e1 = __fsub_rn(s01, d23);
-    e2 = __fadd_rn(d01, s23);
-    e3 = __fsub_rn(s23, d01);
-    stage_round2<kHalf>(e0, e1);
-    stage_round2<kHalf>(e2, e3);
-}
-
-// A radix-4 stage whose four inputs e0..e3 sit in four lanes: lane bit `m1` separates e0|e1
-// (and e2|e3), lane bit `m2` separates the pairs.  Every lane forms s = own + partner and
-// d = own - partner with its m1 partner, then adds the d of its m2 partner.  For the lanes
-// holding e1 and e3, d is the negated pair difference, which is exactly the sign the outputs
-// o1 = s01 - d23 and o3 = s23 - d01 want, so one formula serves all four lanes.
-template <bool kHalf>
-__device__ __forceinline__ void cross_stage(float (&v)[8], int m1, int m2) {
-#pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-        float p0 = __shfl_xor_sync(kFull, v[e], m1), p1 = __shfl_xor_sync(kFull, v[e + 1], m1);
-        float s0 = __fadd_rn(v[e], p0), s1 = __fadd_rn(v[e + 1], p1);
-        float d0 = __fsub_rn(v[e], p0), d1 = __fsub_rn(v[e + 1], p1);
-        float q0 = __shfl_xor_sync(kFull, d0, m2), q1 = __shfl_xor_sync(kFull, d1, m2);
-        v[e] = __fadd_rn(s0, q0);
-        v[e + 1] = __fadd_rn(s1, q1);
-        stage_round2<kHalf>(v[e], v[e + 1]);
-    }
-}
-
-// The group-256 Hadamard of the 8 x 32 values a warp holds (position 8*lane + e), strides
-// 1, 4, 16, 64 (kernels/prepare_norm_i8.loom:174-309; prepare_plain_i8.loom:82-279 with the
-// f16 rounding after every stage).
-template <bool kHalf>
-__device__ __forceinline__ void hadamard256(float (&v)[8]) {
-    butterfly<kHalf>(v[0], v[1], v[2], v[3]);
-    butterfly<kHalf>(v[4], v[5], v[6], v[7]);
-    // stride 4: e0, e1 = v[c], v[c+4] of the even lane; e2, e3 = the same of the odd lane.
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float s = __fadd_rn(v[c], v[c + 4]);
-        float d = __fsub_rn(v[c], v[c + 4]);
-        float dp = __shfl_xor_sync(kFull, d, 1);
-        v[c] = __fadd_rn(s, dp);
-        v[c + 4] = __fsub_rn(s, dp);
-        stage_round2<kHalf>(v[c], v[c + 4]);
-    }
-    cross_stage<kHalf>(v, 2, 4);
-    cross_stage<kHalf>(v, 8, 16);
+__device__ __forceinline__ uint32_t pack_f16x2(F2 v) {
+    __half2 h = __floats2half2_rn(v.a, v.b);
+    return *reinterpret_cast<uint32_t *>(&h);
 }
 
 // Four i32 to four saturated int8, first value in the low byte.
@@ -130,172 +112,547 @@ __device__ __forceinline__ uint32_t pack_s8x4(int x0, int x1, int x2, int x3) {
     return out;
 }
 
-__device__ __forceinline__ float block_max(float value, float *scratch, int lane, int warp) {
+// ---------------------------------------------------------------- thread layout
+// Chunk c of a group (its index bits 3-7) is split as c = c0 + 2 c1 + 4 c2 + 8 c3 + 16 c4:
+// c0, c2, c4 are lane bits 0-2, c1 and c3 live in the thread, lane bits 3-4 and the warp pick
+// the pair of groups.  `first_chunk` is the chunk of the first group at c1 = c3 = 0; the
+// second group lies 32 chunks further on.
+struct Layout {
+    int first_chunk;
+    __device__ __forceinline__ int chunk(int group, int c3, int c1) const {
+        return first_chunk + 32 * group + 8 * c3 + 2 * c1;
+    }
+};
+
+__device__ __forceinline__ Layout make_layout(int warp_in_worker, int lane) {
+    const int pair = warp_in_worker * 4 + (lane >> 3);
+    return Layout{pair * 64 + (lane & 1) + 4 * ((lane >> 1) & 1) + 16 * ((lane >> 2) & 1)};
+}
+
+// Row staging in shared memory: chunk i sits in slot i ^ 2*(bit 4 of i), so that the eight
+// lanes of a quarter warp (which differ in c0, c2 and c4) hit eight different 16-byte columns.
+__device__ __forceinline__ int staged_slot(int chunk) { return chunk ^ (((chunk >> 4) & 1) << 1); }
+// The same for the staged f32 vectors, whose 16-byte unit u = column / 4 carries c0, c2, c4 in
+// its bits 1, 3, 5: unit u sits in slot u ^ bit 3 ^ 4*bit 5.
+__device__ __forceinline__ int vector_slot(int unit) { return unit ^ ((unit >> 3) & 1) ^ (((unit >> 5) & 1) << 2); }
+
+// ---------------------------------------------------------------- Hadamard, f32 (norm, gated)
+// One radix-4 butterfly on both groups (kernels/prepare_norm_i8.loom:194-201).
+__device__ __forceinline__ void butterfly2(F2 &e0, F2 &e1, F2 &e2, F2 &e3) {
+    F2 s01 = add2(e0, e1), s23 = add2(e2, e3);
+    F2 d01 = sub2(e0, e1), d23 = sub2(e2, e3);
+    e0 = add2(s01, d23);
+    e1 = sub2(s01, d23);
+    e2 = add2(d01, s23);
+    e3 = sub2(s23, d01);
+}
+
+// A radix-4 stage whose low digit is in the thread (`lo`, `hi`) and whose high digit is the
+// lane bit `mask`: the lane computes the sum and difference of its own pair and receives the
+// partner's difference.  For the lane holding e2, e3 the received value is d01 and its own sum is
+// s23, and o2 = d01 + s23, o3 = s23 - d01 are the same two expressions.
+__device__ __forceinline__ void split_stage(F2 &lo, F2 &hi, int mask) {
+    F2 s = add2(lo, hi), d = sub2(lo, hi);
+    F2 dp = shfl2(d, mask);
+    lo = add2(s, dp);
+    hi = sub2(s, dp);
+}
+
+// The group-256 Hadamard of the thread's two groups, strides 1, 4, 16, 64
+// (kernels/prepare_norm_i8.loom:174-309).  x[c3][c1][e]: position e + 16 c1 + 64 c3 (+ lanes).
+__device__ __forceinline__ void hadamard256(F2 (&x)[2][2][8]) {
+#pragma unroll
+    for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+        for (int c1 = 0; c1 < 2; c1++) {
+            butterfly2(x[c3][c1][0], x[c3][c1][1], x[c3][c1][2], x[c3][c1][3]);
+            butterfly2(x[c3][c1][4], x[c3][c1][5], x[c3][c1][6], x[c3][c1][7]);
+#pragma unroll
+            for (int c = 0; c < 4; c++) split_stage(x[c3][c1][c], x[c3][c1][c + 4], 1);  // strides 4 | 8
+        }
+#pragma unroll
+    for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) split_stage(x[c3][0][e], x[c3][1][e], 2);  // strides 16 | 32
+#pragma unroll
+    for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) split_stage(x[0][c1][e], x[1][c1][e], 4);  // strides 64 | 128
+}
+
+// ---------------------------------------------------------------- absmax and codes
+__device__ __forceinline__ float warp_max(float value) {
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) value = fmaxf(value, __shfl_xor_sync(kFull, value, off));
-    if (lane == 0) scratch[warp] = value;
-    __syncthreads();
-    float m = scratch[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) m = fmaxf(m, scratch[i]);
-    return m;
+    return value;
 }
 
-// absmax -> scale -> packed codes (kernels/prepare_norm_i8.loom:312-372).  `rotation` is what
-// is left of the orthonormal 1/16 after the stages: 1/16 for the f32 rotation, 16 for the
-// f16 one whose stages already divided by 4 each.
-template <int CPL>
-__device__ __forceinline__ void quantise_and_store(float (&v)[CPL][8], float rotation, int8_t *q_row,
-                                                   float *q_scale, size_t row, float *scratch, int t) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < CPL; j++)
-#pragma unroll
-        for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(v[j][e]));
-    amax = block_max(amax, scratch, t & 31, t >> 5);
+// scale and its reciprocal from the row absmax (kernels/prepare_norm_i8.loom:312-330).  `rotation`
+// is what is left of the orthonormal 1/16 after the stages: 1/16 for the f32 rotation, 16 for
+// the f16 one whose stages already divided by 4 each.
+__device__ __forceinline__ void row_scale(float amax, float rotation, float &s, float &inv) {
     float row_max = __fmul_rn(amax, rotation);
     float safe = fmaxf(row_max, 1.0000000000000001e-30f);
-    float s = __fdiv_rn(safe, 127.0f);
-    float inv = __fdiv_rn(rotation, s);
+    s = __fdiv_rn(safe, 127.0f);
+    inv = __fdiv_rn(rotation, s);
+}
+
+// Eight values of each group to eight codes each (:331-372).  max(x, -127) before rounding
+// equals the clamp after it (-127 is an integer) and sends a NaN to -127 as the reference's
+// maxnum does; the saturating pack clamps at +127.
+__device__ __forceinline__ void store_codes(const F2 (&v)[8], float inv, int8_t *first, int8_t *second) {
+    int ca[8], cb[8];
 #pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        // max(x, -127) before rounding equals the clamp after it (-127 is an integer) and sends a
-        // NaN to -127 as the reference's maxnum does; the saturating pack clamps at +127.
-        int code[8];
-#pragma unroll
-        for (int e = 0; e < 8; e++) code[e] = __float2int_rn(fmaxf(__fmul_rn(v[j][e], inv), -127.0f));
-        *reinterpret_cast<uint2 *>(q_row + 8 * (j * kThreads + t)) =
-            make_uint2(pack_s8x4(code[0], code[1], code[2], code[3]), pack_s8x4(code[4], code[5], code[6], code[7]));
+    for (int e = 0; e < 8; e++) {
+        F2 t = mul2(v[e], both(inv));
+        ca[e] = __float2int_rn(fmaxf(t.a, -127.0f));
+        cb[e] = __float2int_rn(fmaxf(t.b, -127.0f));
     }
-    if (t == 0) q_scale[row] = s;
+    *reinterpret_cast<uint2 *>(first) = make_uint2(pack_s8x4(ca[0], ca[1], ca[2], ca[3]), pack_s8x4(ca[4], ca[5], ca[6], ca[7]));
+    *reinterpret_cast<uint2 *>(second) = make_uint2(pack_s8x4(cb[0], cb[1], cb[2], cb[3]), pack_s8x4(cb[4], cb[5], cb[6], cb[7]));
+}
+
+// Row absmax over the worker (per-warp maxima in `slots`, double-buffered by the caller),
+// then the codes of the thread's 64 positions and the row scale.
+template <int CPL>
+__device__ __forceinline__ void quantise_f32(F2 (&x)[2][2][8], float *slots, int worker, int warp_in_worker,
+                                             int lane, const Layout &layout, int8_t *q_row, float *scale_out) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+        for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) amax = fmaxf(amax, fmaxf(fabsf(x[c3][c1][e].a), fabsf(x[c3][c1][e].b)));
+    amax = warp_max(amax);
+    if (lane == 0) slots[warp_in_worker] = amax;
+    worker_barrier(worker, 32 * CPL);
+    float m = slots[0];
+#pragma unroll
+    for (int i = 1; i < CPL; i++) m = fmaxf(m, slots[i]);
+    float s, inv;
+    row_scale(m, 0.0625f, s, inv);
+#pragma unroll
+    for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+        for (int c1 = 0; c1 < 2; c1++)
+            store_codes(x[c3][c1], inv, q_row + 8 * layout.chunk(0, c3, c1), q_row + 8 * layout.chunk(1, c3, c1));
+    if (warp_in_worker == 0 && lane == 0) *scale_out = s;
+}
+
+// The rows of one block and of one worker in it: blocks split the rows evenly, workers
+// interleave inside a block.
+struct Rows {
+    size_t next, end;
+};
+__device__ __forceinline__ Rows worker_rows(size_t tokens, int worker) {
+    const size_t first = tokens * blockIdx.x / gridDim.x, last = tokens * (blockIdx.x + 1) / gridDim.x;
+    return Rows{first + worker, last};
+}
+
+// ---------------------------------------------------------------- prepare_norm_i8
+template <int CPL>
+struct NormPlan {
+    using G = Geometry<CPL, kWideThreads>;
+    static constexpr int kRowBytes = G::kWorkers * G::kWidth * 2;
+    static constexpr int kSmallBytes = G::kWorkers * (8 + 2 * 16) * 4;
+    static constexpr int kVectorBytes = 3 * G::kWidth * 4;
+    static constexpr bool kStaged = kVectorBytes + kRowBytes + kSmallBytes <= kSmemLimit;
+    static constexpr int kBytes = (kStaged ? kVectorBytes : 0) + kRowBytes + kSmallBytes;
+};
+
+// adaLN on the eight columns of one chunk (kernels/prepare_norm_i8.loom:152-168): bf16 after the
+// norm scale, bf16 of (1 + mod_scale), bf16 of the product, bf16 after the shift.  `one_plus_norm`
+// is 1 + norm_scale, `modulation` is bf16(1 + mod_scale), both per column.
+__device__ __forceinline__ void adaln_chunk(const uint4 &raw, float rinv, const float *one_plus_norm,
+                                            const float *modulation, const float *shift, float (&out)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        F2 n = mul2(mul2(unpack_bf16x2(w[k]), both(rinv)), F2{one_plus_norm[2 * k], one_plus_norm[2 * k + 1]});
+        n = bf_round2(n);
+        F2 s = bf_round2(mul2(n, F2{modulation[2 * k], modulation[2 * k + 1]}));
+        F2 o = bf_round2(add2(s, F2{shift[2 * k], shift[2 * k + 1]}));
+        out[2 * k] = o.a;
+        out[2 * k + 1] = o.b;
+    }
 }
 
 template <int CPL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(Geometry<CPL, kWideThreads>::kBlockThreads, 1)
 prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ norm_scale,
                     const float *__restrict__ mod_scale, const float *__restrict__ mod_shift,
-                    int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride, float eps) {
-    constexpr int width = CPL * 2048;
-    __shared__ float wave_sum[8];
-    __shared__ float wave_max[8];
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const size_t row = blockIdx.x;
-    const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
-    uint4 raw[CPL];
-#pragma unroll
-    for (int j = 0; j < CPL; j++) raw[j] = load_stream(src + j * kThreads + t);
-    float v[CPL][8];
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        unpack_bf16(raw[j], v[j]);
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[e] = __fmaf_rn(v[j][e], v[j][e], acc[e]);  // the square of a bf16 is exact in f32
-    }
-    // 8-wide fold, then the wave by xor butterfly, then the eight waves in the reference's
-    // written order (kernels/prepare_norm_i8.loom:101-138).
-    float ss = __fadd_rn(__fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3])),
-                         __fadd_rn(__fadd_rn(acc[4], acc[5]), __fadd_rn(acc[6], acc[7])));
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(kFull, ss, off));
-    if (lane == 0) wave_sum[warp] = ss;
-    __syncthreads();
-    float total = __fadd_rn(__fadd_rn(__fadd_rn(wave_sum[0], wave_sum[4]), __fadd_rn(wave_sum[2], wave_sum[6])),
-                            __fadd_rn(__fadd_rn(wave_sum[1], wave_sum[5]), __fadd_rn(wave_sum[3], wave_sum[7])));
-    float mean_eps = __fadd_rn(__fdiv_rn(total, static_cast<float>(width)), eps);
-    float rinv = __fdiv_rn(1.0f, __fsqrt_rn(mean_eps));
-#pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        const int base = 8 * (j * kThreads + t);
-        float ns[8], ms[8], sh[8];
-        *reinterpret_cast<float4 *>(ns) = __ldg(reinterpret_cast<const float4 *>(norm_scale + base));
-        *reinterpret_cast<float4 *>(ns + 4) = __ldg(reinterpret_cast<const float4 *>(norm_scale + base + 4));
-        *reinterpret_cast<float4 *>(ms) = __ldg(reinterpret_cast<const float4 *>(mod_scale + base));
-        *reinterpret_cast<float4 *>(ms + 4) = __ldg(reinterpret_cast<const float4 *>(mod_scale + base + 4));
-        *reinterpret_cast<float4 *>(sh) = __ldg(reinterpret_cast<const float4 *>(mod_shift + base));
-        *reinterpret_cast<float4 *>(sh + 4) = __ldg(reinterpret_cast<const float4 *>(mod_shift + base + 4));
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-            // :152-168: bf16 after the norm scale, bf16 of (1 + mod_scale), bf16 of the product,
-            // bf16 after the shift.
-            float n0 = __fmul_rn(__fmul_rn(v[j][e], rinv), __fadd_rn(ns[e], 1.0f));
-            float n1 = __fmul_rn(__fmul_rn(v[j][e + 1], rinv), __fadd_rn(ns[e + 1], 1.0f));
-            bf_round2(n0, n1);
-            float m0 = __fadd_rn(ms[e], 1.0f), m1 = __fadd_rn(ms[e + 1], 1.0f);
-            bf_round2(m0, m1);
-            float s0 = __fmul_rn(n0, m0), s1 = __fmul_rn(n1, m1);
-            bf_round2(s0, s1);
-            float o0 = __fadd_rn(s0, sh[e]), o1 = __fadd_rn(s1, sh[e + 1]);
-            bf_round2(o0, o1);
-            v[j][e] = o0;
-            v[j][e + 1] = o1;
+                    int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride, float eps,
+                    size_t tokens) {
+    using G = Geometry<CPL, kWideThreads>;
+    using Plan = NormPlan<CPL>;
+    constexpr int width = G::kWidth;
+    constexpr int kVirtual = (8 + CPL - 1) / CPL;  // reference waves (of 8) a warp sums
+    extern __shared__ __align__(16) uint8_t smem[];
+    float *vec_norm = reinterpret_cast<float *>(smem);
+    float *vec_mod = vec_norm + width;
+    float *vec_shift = vec_mod + width;
+    uint4 *row_store = reinterpret_cast<uint4 *>(smem + (Plan::kStaged ? Plan::kVectorBytes : 0));
+    float *sum_store = reinterpret_cast<float *>(row_store + G::kWorkers * G::kChunks);
+    float *max_store = sum_store + G::kWorkers * 8;
+
+    if constexpr (Plan::kStaged) {
+        for (int c = threadIdx.x * 4; c < width; c += G::kBlockThreads * 4) {
+            float4 ns = __ldg(reinterpret_cast<const float4 *>(norm_scale + c));
+            float4 ms = __ldg(reinterpret_cast<const float4 *>(mod_scale + c));
+            float4 sh = __ldg(reinterpret_cast<const float4 *>(mod_shift + c));
+            F2 m01 = bf_round2(F2{__fadd_rn(ms.x, 1.0f), __fadd_rn(ms.y, 1.0f)});
+            F2 m23 = bf_round2(F2{__fadd_rn(ms.z, 1.0f), __fadd_rn(ms.w, 1.0f)});
+            const int slot = 4 * vector_slot(c / 4);
+            *reinterpret_cast<float4 *>(vec_norm + slot) =
+                make_float4(__fadd_rn(ns.x, 1.0f), __fadd_rn(ns.y, 1.0f), __fadd_rn(ns.z, 1.0f), __fadd_rn(ns.w, 1.0f));
+            *reinterpret_cast<float4 *>(vec_mod + slot) = make_float4(m01.a, m01.b, m23.a, m23.b);
+            *reinterpret_cast<float4 *>(vec_shift + slot) = sh;
         }
-        hadamard256<false>(v[j]);
+        __syncthreads();
     }
-    quantise_and_store<CPL>(v, 0.0625f, q + row * out_stride, q_scale, row, wave_max, t);
+
+    const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
+    const int lane = t & 31, warp = t >> 5;
+    const Layout layout = make_layout(warp, lane);
+    uint4 *row_buf = row_store + worker * G::kChunks;
+    float *sums = sum_store + worker * 8;
+    float *maxes = max_store + worker * 32;
+    int parity = 0;
+
+    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+        const size_t row = rows.next;
+        const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
+        // Sum of squares in the reference's layout: its wave v, lane l, step j owns chunk
+        // j*256 + v*32 + l.  A warp of this worker takes the waves warp, warp + CPL, ...
+        uint4 raw[kVirtual][CPL];
+#pragma unroll
+        for (int i = 0; i < kVirtual; i++) {
+            const int wave = warp + i * CPL;
+            if (wave < 8) {
+#pragma unroll
+                for (int j = 0; j < CPL; j++) raw[i][j] = load_stream(src + j * 256 + wave * 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kVirtual; i++) {
+            const int wave = warp + i * CPL;
+            if (wave < 8) {
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < CPL; j++) {
+                    row_buf[staged_slot(j * 256 + wave * 32 + lane)] = raw[i][j];
+                    const uint32_t w[4] = {raw[i][j].x, raw[i][j].y, raw[i][j].z, raw[i][j].w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        F2 v = unpack_bf16x2(w[k]);  // the square of a bf16 is exact in f32
+                        acc[2 * k] = __fmaf_rn(v.a, v.a, acc[2 * k]);
+                        acc[2 * k + 1] = __fmaf_rn(v.b, v.b, acc[2 * k + 1]);
+                    }
+                }
+                // 8-wide fold, then the wave by xor butterfly (kernels/prepare_norm_i8.loom:101-125).
+                float ss = __fadd_rn(__fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3])),
+                                     __fadd_rn(__fadd_rn(acc[4], acc[5]), __fadd_rn(acc[6], acc[7])));
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(kFull, ss, off));
+                if (lane == 0) sums[wave] = ss;
+            }
+        }
+        worker_barrier(worker, G::kWorkerThreads);
+        // The eight waves in the reference's written order (:126-138).
+        float total = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[4]), __fadd_rn(sums[2], sums[6])),
+                                __fadd_rn(__fadd_rn(sums[1], sums[5]), __fadd_rn(sums[3], sums[7])));
+        float mean_eps = __fadd_rn(__fdiv_rn(total, static_cast<float>(width)), eps);
+        float rinv = __fdiv_rn(1.0f, __fsqrt_rn(mean_eps));
+
+        F2 x[2][2][8];
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+                for (int group = 0; group < 2; group++) {
+                    const int chunk = layout.chunk(group, c3, c1), col = chunk * 8;
+                    const uint4 packed = row_buf[staged_slot(chunk)];
+                    float o[8];
+                    if constexpr (Plan::kStaged) {
+                        float ns[8], ms[8], sh[8];
+                        const int lo = 4 * vector_slot(2 * chunk), hi = 4 * vector_slot(2 * chunk + 1);
+                        *reinterpret_cast<float4 *>(ns) = *reinterpret_cast<const float4 *>(vec_norm + lo);
+                        *reinterpret_cast<float4 *>(ns + 4) = *reinterpret_cast<const float4 *>(vec_norm + hi);
+                        *reinterpret_cast<float4 *>(ms) = *reinterpret_cast<const float4 *>(vec_mod + lo);
+                        *reinterpret_cast<float4 *>(ms + 4) = *reinterpret_cast<const float4 *>(vec_mod + hi);
+                        *reinterpret_cast<float4 *>(sh) = *reinterpret_cast<const float4 *>(vec_shift + lo);
+                        *reinterpret_cast<float4 *>(sh + 4) = *reinterpret_cast<const float4 *>(vec_shift + hi);
+                        adaln_chunk(packed, rinv, ns, ms, sh, o);
+                    } else {
+                        float ns[8], ms[8], sh[8];
+                        *reinterpret_cast<float4 *>(ns) = __ldg(reinterpret_cast<const float4 *>(norm_scale + col));
+                        *reinterpret_cast<float4 *>(ns + 4) = __ldg(reinterpret_cast<const float4 *>(norm_scale + col + 4));
+                        *reinterpret_cast<float4 *>(ms) = __ldg(reinterpret_cast<const float4 *>(mod_scale + col));
+                        *reinterpret_cast<float4 *>(ms + 4) = __ldg(reinterpret_cast<const float4 *>(mod_scale + col + 4));
+                        *reinterpret_cast<float4 *>(sh) = __ldg(reinterpret_cast<const float4 *>(mod_shift + col));
+                        *reinterpret_cast<float4 *>(sh + 4) = __ldg(reinterpret_cast<const float4 *>(mod_shift + col + 4));
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2) {
+                            F2 m = bf_round2(F2{__fadd_rn(ms[k], 1.0f), __fadd_rn(ms[k + 1], 1.0f)});
+                            ms[k] = m.a;
+                            ms[k + 1] = m.b;
+                            ns[k] = __fadd_rn(ns[k], 1.0f);
+                            ns[k + 1] = __fadd_rn(ns[k + 1], 1.0f);
+                        }
+                        adaln_chunk(packed, rinv, ns, ms, sh, o);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        if (group == 0) x[c3][c1][e].a = o[e];
+                        else x[c3][c1][e].b = o[e];
+                    }
+                }
+        hadamard256(x);
+        quantise_f32<CPL>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
+    }
 }
 
+// ---------------------------------------------------------------- prepare_gated_i8
+// bf16(sigmoid(g)) of every f16 bit pattern g, filled once per device by the kernel below; the
+// blocks of the prologue copy it into shared memory (or compute it themselves while
+// `g_sigmoid_ready` is still 0, e.g. when another stream's first call is filling it).
+__device__ __align__(16) uint16_t g_sigmoid_table[65536];
+__device__ unsigned g_sigmoid_blocks;
+__device__ int g_sigmoid_ready;
+
+// kernels/prepare_gated_i8.loom:98-102: the f32 sigmoid of the f16 gate, rounded to bf16.
+__device__ __forceinline__ uint16_t sigmoid_entry(unsigned bits) {
+    const __half g = __ushort_as_half(static_cast<unsigned short>(bits));
+    const __nv_bfloat16 r = __float2bfloat16_rn(sigmoid_f32(__half2float(g)));
+    return __bfloat16_as_ushort(r);
+}
+
+__global__ void __launch_bounds__(256) sigmoid_table_kernel() {
+    const unsigned i = blockIdx.x * 256 + threadIdx.x;
+    g_sigmoid_table[i] = sigmoid_entry(i);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned done = atomicAdd(&g_sigmoid_blocks, 1u) + 1u;
+        if (done % gridDim.x == 0) {
+            __threadfence();
+            atomicExch(&g_sigmoid_ready, 1);
+        }
+    }
+}
+
+constexpr int kTableBytes = 65536 * 2;
+
 template <int CPL>
-__global__ void __launch_bounds__(kThreads)
+struct GatedPlan {
+    using G = Geometry<CPL, kWideThreads>;
+    static constexpr int kBytes = kTableBytes + G::kWorkers * 2 * 16 * 4 + 16;
+};
+
+template <int CPL>
+__global__ void __launch_bounds__(Geometry<CPL, kWideThreads>::kBlockThreads, 1)
 prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restrict__ gate,
                      int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride,
-                     size_t gate_stride) {
-    constexpr int width = CPL * 2048;
-    __shared__ float wave_max[8];
-    const int t = threadIdx.x, lane = t & 31;
-    const size_t row = blockIdx.x;
-    const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * width);
-    const uint4 *g_src = reinterpret_cast<const uint4 *>(gate + row * gate_stride);
-    uint4 a_raw[CPL], g_raw[CPL];
-#pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        a_raw[j] = load_stream(a_src + j * kThreads + t);
-        g_raw[j] = load_stream(g_src + j * kThreads + t);
+                     size_t gate_stride, size_t tokens) {
+    using G = Geometry<CPL, kWideThreads>;
+    constexpr int width = G::kWidth;
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint16_t *table = reinterpret_cast<uint16_t *>(smem);
+    float *max_store = reinterpret_cast<float *>(smem + kTableBytes);
+    int *ready = reinterpret_cast<int *>(max_store + G::kWorkers * 32);
+
+    if (threadIdx.x == 0) {
+        int flag;
+        asm volatile("ld.acquire.gpu.s32 %0, [%1];" : "=r"(flag) : "l"(&g_sigmoid_ready) : "memory");
+        *ready = flag;
     }
-    float v[CPL][8];
-#pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        float g[8];
-        unpack_f16(a_raw[j], v[j]);
-        unpack_f16(g_raw[j], g);
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-            // kernels/prepare_gated_i8.loom:94-106
-            float a0 = v[j][e], a1 = v[j][e + 1];
-            bf_round2(a0, a1);
-            float g0 = sigmoid_f32(g[e]), g1 = sigmoid_f32(g[e + 1]);
-            bf_round2(g0, g1);
-            float o0 = __fmul_rn(a0, g0), o1 = __fmul_rn(a1, g1);
-            bf_round2(o0, o1);
-            v[j][e] = o0;
-            v[j][e + 1] = o1;
-        }
-        hadamard256<false>(v[j]);
+    __syncthreads();
+    if (*ready) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(g_sigmoid_table);
+        for (int i = threadIdx.x; i < kTableBytes / 16; i += G::kBlockThreads)
+            reinterpret_cast<uint4 *>(table)[i] = __ldcg(src + i);
+    } else {
+        for (unsigned i = threadIdx.x; i < 65536u; i += G::kBlockThreads) table[i] = sigmoid_entry(i);
     }
-    quantise_and_store<CPL>(v, 0.0625f, q + row * out_stride, q_scale, row, wave_max, t);
+    __syncthreads();
+
+    const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
+    const int lane = t & 31, warp = t >> 5;
+    const Layout layout = make_layout(warp, lane);
+    float *maxes = max_store + worker * 32;
+    int parity = 0;
+
+    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+        const size_t row = rows.next;
+        const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * width);
+        const uint4 *g_src = reinterpret_cast<const uint4 *>(gate + row * gate_stride);
+        uint4 a_raw[2][2][2], g_raw[2][2][2];
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+                for (int group = 0; group < 2; group++) {
+                    a_raw[c3][c1][group] = load_stream(a_src + layout.chunk(group, c3, c1));
+                    g_raw[c3][c1][group] = load_stream(g_src + layout.chunk(group, c3, c1));
+                }
+        F2 x[2][2][8];
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+                for (int group = 0; group < 2; group++) {
+                    const uint4 &ar = a_raw[c3][c1][group], &gr = g_raw[c3][c1][group];
+                    const uint32_t aw[4] = {ar.x, ar.y, ar.z, ar.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        // kernels/prepare_gated_i8.loom:94-106
+                        F2 a = bf_round2(unpack_f16x2(aw[k]));
+                        F2 g = F2{__uint_as_float(static_cast<uint32_t>(table[gw[k] & 0xffffu]) << 16),
+                                  __uint_as_float(static_cast<uint32_t>(table[gw[k] >> 16]) << 16)};
+                        F2 o = bf_round2(mul2(a, g));
+                        if (group == 0) {
+                            x[c3][c1][2 * k].a = o.a;
+                            x[c3][c1][2 * k + 1].a = o.b;
+                        } else {
+                            x[c3][c1][2 * k].b = o.a;
+                            x[c3][c1][2 * k + 1].b = o.b;
+                        }
+                    }
+                }
+        hadamard256(x);
+        quantise_f32<CPL>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
+    }
+}
+
+// ---------------------------------------------------------------- prepare_plain_i8
+// The f16 Hadamard (kernels/prepare_plain_i8.loom:82-279): every stage ends in a quarter and an
+// f16 rounding, so between stages the row is held as f16x2 words, low half = first group.
+__device__ __forceinline__ uint32_t quarter_f16x2(F2 v) { return pack_f16x2(mul2(v, both(0.25f))); }
+
+__device__ __forceinline__ void split_stage_f16(uint32_t &lo, uint32_t &hi, int mask) {
+    F2 a = unpack_f16x2(lo), b = unpack_f16x2(hi);
+    F2 s = add2(a, b), d = sub2(a, b);
+    F2 dp = shfl2(d, mask);
+    lo = quarter_f16x2(add2(s, dp));
+    hi = quarter_f16x2(sub2(s, dp));
 }
 
 template <int CPL>
-__global__ void __launch_bounds__(kThreads)
+struct PlainPlan {
+    using G = Geometry<CPL, kPlainThreads>;
+    static constexpr int kBytes = G::kWorkers * 2 * 16 * 4;
+};
+
+template <int CPL>
+__global__ void __launch_bounds__(Geometry<CPL, kPlainThreads>::kBlockThreads, 1)
 prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, float *__restrict__ q_scale,
-                     size_t out_stride) {
-    constexpr int width = CPL * 2048;
-    __shared__ float wave_max[8];
-    const int t = threadIdx.x, lane = t & 31;
-    const size_t row = blockIdx.x;
-    const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
-    uint4 raw[CPL];
+                     size_t out_stride, size_t tokens) {
+    using G = Geometry<CPL, kPlainThreads>;
+    constexpr int width = G::kWidth;
+    extern __shared__ __align__(16) uint8_t smem[];
+    float *max_store = reinterpret_cast<float *>(smem);
+    const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
+    const int lane = t & 31, warp = t >> 5;
+    const Layout layout = make_layout(warp, lane);
+    float *maxes = max_store + worker * 32;
+    int parity = 0;
+
+    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+        const size_t row = rows.next;
+        const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
+        uint4 raw[2][2][2];
 #pragma unroll
-    for (int j = 0; j < CPL; j++) raw[j] = load_stream(src + j * kThreads + t);
-    float v[CPL][8];
+        for (int c3 = 0; c3 < 2; c3++)
 #pragma unroll
-    for (int j = 0; j < CPL; j++) {
-        unpack_f16(raw[j], v[j]);
-        hadamard256<true>(v[j]);
+            for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+                for (int group = 0; group < 2; group++) raw[c3][c1][group] = load_stream(src + layout.chunk(group, c3, c1));
+        uint32_t x[2][2][8];
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++) {
+                const uint4 &ra = raw[c3][c1][0], &rb = raw[c3][c1][1];
+                const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
+                F2 e[8];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const F2 fa = unpack_f16x2(aw[k]), fb = unpack_f16x2(bw[k]);
+                    e[2 * k] = F2{fa.a, fb.a};
+                    e[2 * k + 1] = F2{fa.b, fb.b};
+                }
+                butterfly2(e[0], e[1], e[2], e[3]);
+                butterfly2(e[4], e[5], e[6], e[7]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) x[c3][c1][k] = quarter_f16x2(e[k]);
+#pragma unroll
+                for (int c = 0; c < 4; c++) split_stage_f16(x[c3][c1][c], x[c3][c1][c + 4], 1);
+            }
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) split_stage_f16(x[c3][0][e], x[c3][1][e], 2);
+#pragma unroll
+        for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) split_stage_f16(x[0][c1][e], x[1][c1][e], 4);
+
+        // absmax on the packed halves (exact: a maximum of f16 values), then as in the f32 prologues.
+        __half2 packed_max = __float2half2_rn(0.0f);
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++)
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    packed_max = __hmax2(packed_max, __habs2(*reinterpret_cast<const __half2 *>(&x[c3][c1][e])));
+        float amax = warp_max(fmaxf(__low2float(packed_max), __high2float(packed_max)));
+        if (lane == 0) maxes[parity + warp] = amax;
+        worker_barrier(worker, G::kWorkerThreads);
+        float m = maxes[parity];
+#pragma unroll
+        for (int i = 1; i < CPL; i++) m = fmaxf(m, maxes[parity + i]);
+        float s, inv;
+        row_scale(m, 16.0f, s, inv);
+        int8_t *q_row = q + row * out_stride;
+#pragma unroll
+        for (int c3 = 0; c3 < 2; c3++)
+#pragma unroll
+            for (int c1 = 0; c1 < 2; c1++) {
+                F2 v[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = unpack_f16x2(x[c3][c1][e]);
+                store_codes(v, inv, q_row + 8 * layout.chunk(0, c3, c1), q_row + 8 * layout.chunk(1, c3, c1));
+            }
+        if (warp == 0 && lane == 0) q_scale[row] = s;
     }
-    quantise_and_store<CPL>(v, 16.0f, q + row * out_stride, q_scale, row, wave_max, t);
 }
 
+__device__ __forceinline__ void unpack_bf16(const uint4 &raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const F2 f = unpack_bf16x2(w[i]);
+        v[2 * i] = f.a;
+        v[2 * i + 1] = f.b;
+    }
+}
+
+__device__ __forceinline__ void unpack_f16(const uint4 &raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const F2 f = unpack_f16x2(w[i]);
+        v[2 * i] = f.a;
+        v[2 * i + 1] = f.b;
+    }
+}
+
+// ---------------------------------------------------------------- launches
 template <template <int> class Launch, typename... Args>
 int dispatch_width(size_t width, Args... args) {
     switch (width / 2048) {
@@ -314,31 +671,97 @@ int finish_launch(const char *what) {
     return KREA2_OK;
 }
 
+constexpr int kMaxDevices = 64;
+
+int current_device(int *device) {
+    KREA2_CUDA(cudaGetDevice(device));
+    if (*device < 0 || *device >= kMaxDevices) return fail(KREA2_INTERNAL, "device index %d out of range", *device);
+    return KREA2_OK;
+}
+
+int device_sms(int device) {
+    static std::atomic<int> cached[kMaxDevices];
+    int n = cached[device].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+// Raises a kernel's dynamic shared-memory limit on first use per device (not a stream operation).
+template <typename Kernel>
+int allow_shared(Kernel kernel, int bytes, std::atomic<bool> (&done)[kMaxDevices], int device) {
+    if (!done[device].load(std::memory_order_acquire)) {
+        KREA2_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        done[device].store(true, std::memory_order_release);
+    }
+    return KREA2_OK;
+}
+
+unsigned persistent_grid(int device, size_t tokens, int workers) {
+    const size_t wanted = (tokens + workers - 1) / workers, sms = static_cast<size_t>(device_sms(device));
+    return static_cast<unsigned>(wanted < sms ? wanted : sms);
+}
+
 template <int CPL>
 struct LaunchNorm {
     static int run(cudaStream_t stream, size_t tokens, const void *h, const float *ns, const float *ms,
                    const float *sh, void *q, float *q_scale, size_t out_stride, float eps) {
-        prepare_norm_kernel<CPL><<<static_cast<unsigned>(tokens), kThreads, 0, stream>>>(
-            static_cast<const uint16_t *>(h), ns, ms, sh, static_cast<int8_t *>(q), q_scale, out_stride, eps);
+        using G = Geometry<CPL, kWideThreads>;
+        static std::atomic<bool> done[kMaxDevices];
+        int device = 0;
+        if (int s = current_device(&device)) return s;
+        if (int s = allow_shared(prepare_norm_kernel<CPL>, NormPlan<CPL>::kBytes, done, device)) return s;
+        prepare_norm_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
+                                   NormPlan<CPL>::kBytes, stream>>>(
+            static_cast<const uint16_t *>(h), ns, ms, sh, static_cast<int8_t *>(q), q_scale, out_stride, eps, tokens);
         return finish_launch("prepare_norm_i8");
     }
 };
+
+// The sigmoid table is filled by the first gated call on a device, on that call's stream; calls
+// on other streams that overtake the fill compute the table in the kernel instead.
+int ensure_sigmoid_table(cudaStream_t stream, int device) {
+    static std::atomic<bool> launched[kMaxDevices];
+    if (!launched[device].exchange(true, std::memory_order_acq_rel)) {
+        sigmoid_table_kernel<<<256, 256, 0, stream>>>();
+        if (int s = finish_launch("sigmoid table")) {
+            launched[device].store(false, std::memory_order_release);
+            return s;
+        }
+    }
+    return KREA2_OK;
+}
+
 template <int CPL>
 struct LaunchGated {
     static int run(cudaStream_t stream, size_t tokens, const void *attn, const void *gate, void *q,
                    float *q_scale, size_t out_stride, size_t gate_stride) {
-        prepare_gated_kernel<CPL><<<static_cast<unsigned>(tokens), kThreads, 0, stream>>>(
+        using G = Geometry<CPL, kWideThreads>;
+        static std::atomic<bool> done[kMaxDevices];
+        int device = 0;
+        if (int s = current_device(&device)) return s;
+        if (int s = allow_shared(prepare_gated_kernel<CPL>, GatedPlan<CPL>::kBytes, done, device)) return s;
+        if (int s = ensure_sigmoid_table(stream, device)) return s;
+        prepare_gated_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
+                                    GatedPlan<CPL>::kBytes, stream>>>(
             static_cast<const uint16_t *>(attn), static_cast<const uint16_t *>(gate), static_cast<int8_t *>(q),
-            q_scale, out_stride, gate_stride);
+            q_scale, out_stride, gate_stride, tokens);
         return finish_launch("prepare_gated_i8");
     }
 };
+
 template <int CPL>
 struct LaunchPlain {
     static int run(cudaStream_t stream, size_t tokens, const void *h, void *q, float *q_scale,
                    size_t out_stride) {
-        prepare_plain_kernel<CPL><<<static_cast<unsigned>(tokens), kThreads, 0, stream>>>(
-            static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride);
+        using G = Geometry<CPL, kPlainThreads>;
+        int device = 0;
+        if (int s = current_device(&device)) return s;
+        prepare_plain_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
+                                    PlainPlan<CPL>::kBytes, stream>>>(
+            static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride, tokens);
         return finish_launch("prepare_plain_i8");
     }
 };
