@@ -27,7 +27,7 @@ namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kSmemLimit = 232448;       // opt-in dynamic shared memory of one sm_100 block
-constexpr int kWideThreads = 576;        // block size limit of the f32 prologues (112 registers)
+constexpr int kWideThreads = 576;        // block size limit of the f32 prologues (96 registers)
 constexpr int kPlainThreads = 768;       // of the f16 prologue, which keeps its row packed
 
 template <int CPL, int MAX_THREADS>
@@ -52,6 +52,14 @@ __device__ __forceinline__ uint4 load_stream(const uint4 *p) {
 __device__ __forceinline__ void worker_barrier(int worker, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(worker + 1), "r"(threads) : "memory");
 }
+
+__device__ __forceinline__ void copy_async16(void *shared_dst, const void *global_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst))),
+                 "l"(global_src)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // Two f32 values in one 64-bit register pair: `a` belongs to the first group of the thread,
 // `b` to the second (or, in the adaLN arithmetic, to the next column).
@@ -87,6 +95,47 @@ __device__ __forceinline__ F2 unpack_bf16x2(uint32_t w) {
 __device__ __forceinline__ F2 unpack_f16x2(uint32_t w) {
     const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
     return F2{f.x, f.y};
+}
+
+// The mixed-precision forms below read a 16-bit operand as the IEEE value it encodes and do one
+// f32 operation with one rounding, so each equals the convert-then-operate sequence it replaces
+// (every bf16 or f16 value is an f32 value).
+// f32(h) * 0.25 for both halves of an f16x2 word: the f16 stage scale folded into the unpack.  A
+// power-of-two scale commutes with every later rounding of the stage, nothing being near the f32
+// or f16 underflow range after it (|x| >= 2^-26 or zero).
+__device__ __forceinline__ F2 unpack_quarter_f16x2(uint32_t w) {
+    F2 d;
+    asm("{ .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n fma.rn.f32.f16 %0, lo, %3, %4;\n fma.rn.f32.f16 %1, hi, %3, %4;\n }"
+        : "=f"(d.a), "=f"(d.b)
+        : "r"(w), "h"(static_cast<unsigned short>(0x3400)), "f"(-0.0f));
+    return d;
+}
+// acc + x*x for both bf16 halves of w.
+__device__ __forceinline__ void square_accumulate_bf16x2(uint32_t w, float &lo_acc, float &hi_acc) {
+    asm("{ .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n fma.rn.f32.bf16 %0, lo, lo, %0;\n fma.rn.f32.bf16 %1, hi, hi, %1;\n }"
+        : "+f"(lo_acc), "+f"(hi_acc)
+        : "r"(w));
+}
+// The f32 products of the halves of two bf16x2 words (x*y + -0 is the rounded product, signed zeros kept).
+__device__ __forceinline__ F2 product_bf16x2(uint32_t x, uint32_t y) {
+    F2 d;
+    asm("{ .reg .b16 xl, xh, yl, yh;\n mov.b32 {xl, xh}, %2;\n mov.b32 {yl, yh}, %3;\n"
+        " fma.rn.f32.bf16 %0, xl, yl, %4;\n fma.rn.f32.bf16 %1, xh, yh, %4;\n }"
+        : "=f"(d.a), "=f"(d.b)
+        : "r"(x), "r"(y), "f"(-0.0f));
+    return d;
+}
+// The halves of a bf16x2 word plus two f32 addends.
+__device__ __forceinline__ F2 add_bf16x2(uint32_t x, F2 addend) {
+    F2 d;
+    asm("{ .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n add.rn.f32.bf16 %0, lo, %3;\n add.rn.f32.bf16 %1, hi, %4;\n }"
+        : "=f"(d.a), "=f"(d.b)
+        : "r"(x), "f"(addend.a), "f"(addend.b));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(F2 v) {
+    __nv_bfloat162 packed = __floats2bfloat162_rn(v.a, v.b);
+    return *reinterpret_cast<uint32_t *>(&packed);
 }
 
 // bf16 rounding of both halves with one packed conversion (cvt.rn.bf16x2.f32).
@@ -254,25 +303,25 @@ __device__ __forceinline__ Rows worker_rows(size_t tokens, int worker) {
 template <int CPL>
 struct NormPlan {
     using G = Geometry<CPL, kWideThreads>;
-    static constexpr int kRowBytes = G::kWorkers * G::kWidth * 2;
+    static constexpr int kRowBytes = 2 * G::kWorkers * G::kWidth * 2;  // two buffers per worker
     static constexpr int kSmallBytes = G::kWorkers * (8 + 2 * 16) * 4;
-    static constexpr int kVectorBytes = 3 * G::kWidth * 4;
+    static constexpr int kVectorBytes = G::kWidth * (4 + 4 + 2);
     static constexpr bool kStaged = kVectorBytes + kRowBytes + kSmallBytes <= kSmemLimit;
     static constexpr int kBytes = (kStaged ? kVectorBytes : 0) + kRowBytes + kSmallBytes;
 };
 
 // adaLN on the eight columns of one chunk (kernels/prepare_norm_i8.loom:152-168): bf16 after the
 // norm scale, bf16 of (1 + mod_scale), bf16 of the product, bf16 after the shift.  `one_plus_norm`
-// is 1 + norm_scale, `modulation` is bf16(1 + mod_scale), both per column.
+// is 1 + norm_scale per column, `modulation` the bf16x2 words of bf16(1 + mod_scale).
 __device__ __forceinline__ void adaln_chunk(const uint4 &raw, float rinv, const float *one_plus_norm,
-                                            const float *modulation, const float *shift, float (&out)[8]) {
+                                            const uint32_t *modulation, const float *shift, float (&out)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-        F2 n = mul2(mul2(unpack_bf16x2(w[k]), both(rinv)), F2{one_plus_norm[2 * k], one_plus_norm[2 * k + 1]});
-        n = bf_round2(n);
-        F2 s = bf_round2(mul2(n, F2{modulation[2 * k], modulation[2 * k + 1]}));
-        F2 o = bf_round2(add2(s, F2{shift[2 * k], shift[2 * k + 1]}));
+        const uint32_t n = pack_bf16x2(
+            mul2(mul2(unpack_bf16x2(w[k]), both(rinv)), F2{one_plus_norm[2 * k], one_plus_norm[2 * k + 1]}));
+        const uint32_t s = pack_bf16x2(product_bf16x2(n, modulation[k]));
+        const F2 o = bf_round2(add_bf16x2(s, F2{shift[2 * k], shift[2 * k + 1]}));
         out[2 * k] = o.a;
         out[2 * k + 1] = o.b;
     }
@@ -290,24 +339,29 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     constexpr int kVirtual = (8 + CPL - 1) / CPL;  // reference waves (of 8) a warp sums
     extern __shared__ __align__(16) uint8_t smem[];
     float *vec_norm = reinterpret_cast<float *>(smem);
-    float *vec_mod = vec_norm + width;
-    float *vec_shift = vec_mod + width;
+    float *vec_shift = vec_norm + width;
+    uint4 *vec_mod = reinterpret_cast<uint4 *>(vec_shift + width);  // one 16-byte unit per chunk
     uint4 *row_store = reinterpret_cast<uint4 *>(smem + (Plan::kStaged ? Plan::kVectorBytes : 0));
-    float *sum_store = reinterpret_cast<float *>(row_store + G::kWorkers * G::kChunks);
+    float *sum_store = reinterpret_cast<float *>(row_store + 2 * G::kWorkers * G::kChunks);
     float *max_store = sum_store + G::kWorkers * 8;
 
     if constexpr (Plan::kStaged) {
-        for (int c = threadIdx.x * 4; c < width; c += G::kBlockThreads * 4) {
-            float4 ns = __ldg(reinterpret_cast<const float4 *>(norm_scale + c));
-            float4 ms = __ldg(reinterpret_cast<const float4 *>(mod_scale + c));
-            float4 sh = __ldg(reinterpret_cast<const float4 *>(mod_shift + c));
-            F2 m01 = bf_round2(F2{__fadd_rn(ms.x, 1.0f), __fadd_rn(ms.y, 1.0f)});
-            F2 m23 = bf_round2(F2{__fadd_rn(ms.z, 1.0f), __fadd_rn(ms.w, 1.0f)});
-            const int slot = 4 * vector_slot(c / 4);
-            *reinterpret_cast<float4 *>(vec_norm + slot) =
-                make_float4(__fadd_rn(ns.x, 1.0f), __fadd_rn(ns.y, 1.0f), __fadd_rn(ns.z, 1.0f), __fadd_rn(ns.w, 1.0f));
-            *reinterpret_cast<float4 *>(vec_mod + slot) = make_float4(m01.a, m01.b, m23.a, m23.b);
-            *reinterpret_cast<float4 *>(vec_shift + slot) = sh;
+        for (int chunk = threadIdx.x; chunk < G::kChunks; chunk += G::kBlockThreads) {
+            const int c = chunk * 8;
+            uint32_t m[4];
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float4 ns = __ldg(reinterpret_cast<const float4 *>(norm_scale + c + 4 * half));
+                float4 ms = __ldg(reinterpret_cast<const float4 *>(mod_scale + c + 4 * half));
+                float4 sh = __ldg(reinterpret_cast<const float4 *>(mod_shift + c + 4 * half));
+                const int slot = 4 * vector_slot(2 * chunk + half);
+                *reinterpret_cast<float4 *>(vec_norm + slot) = make_float4(
+                    __fadd_rn(ns.x, 1.0f), __fadd_rn(ns.y, 1.0f), __fadd_rn(ns.z, 1.0f), __fadd_rn(ns.w, 1.0f));
+                *reinterpret_cast<float4 *>(vec_shift + slot) = sh;
+                m[2 * half] = pack_bf16x2(F2{__fadd_rn(ms.x, 1.0f), __fadd_rn(ms.y, 1.0f)});
+                m[2 * half + 1] = pack_bf16x2(F2{__fadd_rn(ms.z, 1.0f), __fadd_rn(ms.w, 1.0f)});
+            }
+            vec_mod[staged_slot(chunk)] = make_uint4(m[0], m[1], m[2], m[3]);
         }
         __syncthreads();
     }
@@ -315,25 +369,33 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
-    uint4 *row_buf = row_store + worker * G::kChunks;
+    uint4 *row_bufs = row_store + 2 * worker * G::kChunks;
     float *sums = sum_store + worker * 8;
     float *maxes = max_store + worker * 32;
     int parity = 0;
 
-    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
-        const size_t row = rows.next;
+    // The next row streams into the worker's other buffer (16-byte asynchronous copies, slot-swizzled)
+    // while this one is worked on; the wait for it sits in front of a barrier the row needs anyway.
+    auto fetch = [&](size_t row, int buffer) {
         const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
+        uint4 *dst = row_bufs + buffer * G::kChunks;
+#pragma unroll
+        for (int i = 0; i < 8; i++) copy_async16(dst + staged_slot(t + i * G::kWorkerThreads), src + t + i * G::kWorkerThreads);
+        copy_async_commit();
+    };
+    Rows rows = worker_rows(tokens, worker);
+    if (rows.next < rows.end) {
+        fetch(rows.next, 0);
+        copy_async_wait();
+    }
+    worker_barrier(worker, G::kWorkerThreads);
+
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+        const size_t row = rows.next;
+        const uint4 *row_buf = row_bufs + (parity ? G::kChunks : 0);
+        if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, parity ? 0 : 1);
         // Sum of squares in the reference's layout: its wave v, lane l, step j owns chunk
         // j*256 + v*32 + l.  A warp of this worker takes the waves warp, warp + CPL, ...
-        uint4 raw[kVirtual][CPL];
-#pragma unroll
-        for (int i = 0; i < kVirtual; i++) {
-            const int wave = warp + i * CPL;
-            if (wave < 8) {
-#pragma unroll
-                for (int j = 0; j < CPL; j++) raw[i][j] = load_stream(src + j * 256 + wave * 32 + lane);
-            }
-        }
 #pragma unroll
         for (int i = 0; i < kVirtual; i++) {
             const int wave = warp + i * CPL;
@@ -341,14 +403,11 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
                 for (int j = 0; j < CPL; j++) {
-                    row_buf[staged_slot(j * 256 + wave * 32 + lane)] = raw[i][j];
-                    const uint32_t w[4] = {raw[i][j].x, raw[i][j].y, raw[i][j].z, raw[i][j].w};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        F2 v = unpack_bf16x2(w[k]);  // the square of a bf16 is exact in f32
-                        acc[2 * k] = __fmaf_rn(v.a, v.a, acc[2 * k]);
-                        acc[2 * k + 1] = __fmaf_rn(v.b, v.b, acc[2 * k + 1]);
-                    }
+                    const uint4 raw = row_buf[staged_slot(j * 256 + wave * 32 + lane)];
+                    square_accumulate_bf16x2(raw.x, acc[0], acc[1]);  // the square of a bf16 is exact in f32
+                    square_accumulate_bf16x2(raw.y, acc[2], acc[3]);
+                    square_accumulate_bf16x2(raw.z, acc[4], acc[5]);
+                    square_accumulate_bf16x2(raw.w, acc[6], acc[7]);
                 }
                 // 8-wide fold, then the wave by xor butterfly (kernels/prepare_norm_i8.loom:101-125).
                 float ss = __fadd_rn(__fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3])),
@@ -374,19 +433,17 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                 for (int group = 0; group < 2; group++) {
                     const int chunk = layout.chunk(group, c3, c1), col = chunk * 8;
                     const uint4 packed = row_buf[staged_slot(chunk)];
-                    float o[8];
+                    float o[8], ns[8], sh[8];
+                    uint32_t m[4];
                     if constexpr (Plan::kStaged) {
-                        float ns[8], ms[8], sh[8];
                         const int lo = 4 * vector_slot(2 * chunk), hi = 4 * vector_slot(2 * chunk + 1);
                         *reinterpret_cast<float4 *>(ns) = *reinterpret_cast<const float4 *>(vec_norm + lo);
                         *reinterpret_cast<float4 *>(ns + 4) = *reinterpret_cast<const float4 *>(vec_norm + hi);
-                        *reinterpret_cast<float4 *>(ms) = *reinterpret_cast<const float4 *>(vec_mod + lo);
-                        *reinterpret_cast<float4 *>(ms + 4) = *reinterpret_cast<const float4 *>(vec_mod + hi);
                         *reinterpret_cast<float4 *>(sh) = *reinterpret_cast<const float4 *>(vec_shift + lo);
                         *reinterpret_cast<float4 *>(sh + 4) = *reinterpret_cast<const float4 *>(vec_shift + hi);
-                        adaln_chunk(packed, rinv, ns, ms, sh, o);
+                        *reinterpret_cast<uint4 *>(m) = vec_mod[staged_slot(chunk)];
                     } else {
-                        float ns[8], ms[8], sh[8];
+                        float ms[8];
                         *reinterpret_cast<float4 *>(ns) = __ldg(reinterpret_cast<const float4 *>(norm_scale + col));
                         *reinterpret_cast<float4 *>(ns + 4) = __ldg(reinterpret_cast<const float4 *>(norm_scale + col + 4));
                         *reinterpret_cast<float4 *>(ms) = __ldg(reinterpret_cast<const float4 *>(mod_scale + col));
@@ -394,15 +451,13 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                         *reinterpret_cast<float4 *>(sh) = __ldg(reinterpret_cast<const float4 *>(mod_shift + col));
                         *reinterpret_cast<float4 *>(sh + 4) = __ldg(reinterpret_cast<const float4 *>(mod_shift + col + 4));
 #pragma unroll
-                        for (int k = 0; k < 8; k += 2) {
-                            F2 m = bf_round2(F2{__fadd_rn(ms[k], 1.0f), __fadd_rn(ms[k + 1], 1.0f)});
-                            ms[k] = m.a;
-                            ms[k + 1] = m.b;
-                            ns[k] = __fadd_rn(ns[k], 1.0f);
-                            ns[k + 1] = __fadd_rn(ns[k + 1], 1.0f);
+                        for (int k = 0; k < 4; k++) {
+                            m[k] = pack_bf16x2(F2{__fadd_rn(ms[2 * k], 1.0f), __fadd_rn(ms[2 * k + 1], 1.0f)});
+                            ns[2 * k] = __fadd_rn(ns[2 * k], 1.0f);
+                            ns[2 * k + 1] = __fadd_rn(ns[2 * k + 1], 1.0f);
                         }
-                        adaln_chunk(packed, rinv, ns, ms, sh, o);
                     }
+                    adaln_chunk(packed, rinv, ns, m, sh, o);
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         if (group == 0) x[c3][c1][e].a = o[e];
@@ -410,6 +465,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                     }
                 }
         hadamard256(x);
+        copy_async_wait();  // the next row: published by the barrier inside quantise_f32
         quantise_f32<CPL>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
     }
 }
@@ -510,10 +566,10 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         // kernels/prepare_gated_i8.loom:94-106
-                        F2 a = bf_round2(unpack_f16x2(aw[k]));
-                        F2 g = F2{__uint_as_float(static_cast<uint32_t>(table[gw[k] & 0xffffu]) << 16),
-                                  __uint_as_float(static_cast<uint32_t>(table[gw[k] >> 16]) << 16)};
-                        F2 o = bf_round2(mul2(a, g));
+                        const uint32_t a = pack_bf16x2(unpack_f16x2(aw[k]));
+                        const uint32_t g = static_cast<uint32_t>(table[gw[k] & 0xffffu]) |
+                                           (static_cast<uint32_t>(table[gw[k] >> 16]) << 16);
+                        F2 o = bf_round2(product_bf16x2(a, g));
                         if (group == 0) {
                             x[c3][c1][2 * k].a = o.a;
                             x[c3][c1][2 * k + 1].a = o.b;
@@ -531,20 +587,21 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
 // ---------------------------------------------------------------- prepare_plain_i8
 // The f16 Hadamard (kernels/prepare_plain_i8.loom:82-279): every stage ends in a quarter and an
 // f16 rounding, so between stages the row is held as f16x2 words, low half = first group.
-__device__ __forceinline__ uint32_t quarter_f16x2(F2 v) { return pack_f16x2(mul2(v, both(0.25f))); }
-
+// A stage scales its inputs by a quarter while unpacking them (see unpack_quarter_f16x2) and
+// rounds its outputs to f16.
 __device__ __forceinline__ void split_stage_f16(uint32_t &lo, uint32_t &hi, int mask) {
-    F2 a = unpack_f16x2(lo), b = unpack_f16x2(hi);
+    F2 a = unpack_quarter_f16x2(lo), b = unpack_quarter_f16x2(hi);
     F2 s = add2(a, b), d = sub2(a, b);
     F2 dp = shfl2(d, mask);
-    lo = quarter_f16x2(add2(s, dp));
-    hi = quarter_f16x2(sub2(s, dp));
+    lo = pack_f16x2(add2(s, dp));
+    hi = pack_f16x2(sub2(s, dp));
 }
 
 template <int CPL>
 struct PlainPlan {
     using G = Geometry<CPL, kPlainThreads>;
-    static constexpr int kBytes = G::kWorkers * 2 * 16 * 4;
+    static constexpr int kStageBytes = 2 * 8 * 16 * G::kBlockThreads;  // two rows of eight chunks per thread
+    static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * 16 * 4;
 };
 
 template <int CPL>
@@ -554,44 +611,54 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
     using G = Geometry<CPL, kPlainThreads>;
     constexpr int width = G::kWidth;
     extern __shared__ __align__(16) uint8_t smem[];
-    float *max_store = reinterpret_cast<float *>(smem);
+    uint4 *stage = reinterpret_cast<uint4 *>(smem);
+    float *max_store = reinterpret_cast<float *>(smem + PlainPlan<CPL>::kStageBytes);
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
     float *maxes = max_store + worker * 32;
     int parity = 0;
 
-    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
-        const size_t row = rows.next;
+    // Each thread streams its own eight chunks of the next row into shared memory while it works
+    // on this one: slot (buffer, piece) of thread x is stage[(buffer*8 + piece) * threads + x].
+    auto fetch = [&](size_t row, int buffer) {
         const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
-        uint4 raw[2][2][2];
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
-#pragma unroll
-            for (int c1 = 0; c1 < 2; c1++)
-#pragma unroll
-                for (int group = 0; group < 2; group++) raw[c3][c1][group] = load_stream(src + layout.chunk(group, c3, c1));
+        for (int piece = 0; piece < 8; piece++)
+            copy_async16(stage + (buffer * 8 + piece) * G::kBlockThreads + threadIdx.x,
+                         src + layout.chunk(piece & 1, piece >> 2, (piece >> 1) & 1));
+        copy_async_commit();
+    };
+    Rows rows = worker_rows(tokens, worker);
+    if (rows.next < rows.end) fetch(rows.next, 0);
+
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+        const size_t row = rows.next;
+        const int buffer = parity ? 1 : 0;
+        copy_async_wait();
         uint32_t x[2][2][8];
 #pragma unroll
         for (int c3 = 0; c3 < 2; c3++)
 #pragma unroll
             for (int c1 = 0; c1 < 2; c1++) {
-                const uint4 &ra = raw[c3][c1][0], &rb = raw[c3][c1][1];
+                const uint4 ra = stage[(buffer * 8 + 4 * c3 + 2 * c1) * G::kBlockThreads + threadIdx.x];
+                const uint4 rb = stage[(buffer * 8 + 4 * c3 + 2 * c1 + 1) * G::kBlockThreads + threadIdx.x];
                 const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
                 F2 e[8];
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
-                    const F2 fa = unpack_f16x2(aw[k]), fb = unpack_f16x2(bw[k]);
+                    const F2 fa = unpack_quarter_f16x2(aw[k]), fb = unpack_quarter_f16x2(bw[k]);
                     e[2 * k] = F2{fa.a, fb.a};
                     e[2 * k + 1] = F2{fa.b, fb.b};
                 }
                 butterfly2(e[0], e[1], e[2], e[3]);
                 butterfly2(e[4], e[5], e[6], e[7]);
 #pragma unroll
-                for (int k = 0; k < 8; k++) x[c3][c1][k] = quarter_f16x2(e[k]);
+                for (int k = 0; k < 8; k++) x[c3][c1][k] = pack_f16x2(e[k]);
 #pragma unroll
                 for (int c = 0; c < 4; c++) split_stage_f16(x[c3][c1][c], x[c3][c1][c + 4], 1);
             }
+        if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, buffer ^ 1);
 #pragma unroll
         for (int c3 = 0; c3 < 2; c3++)
 #pragma unroll
@@ -757,8 +824,10 @@ struct LaunchPlain {
     static int run(cudaStream_t stream, size_t tokens, const void *h, void *q, float *q_scale,
                    size_t out_stride) {
         using G = Geometry<CPL, kPlainThreads>;
+        static std::atomic<bool> done[kMaxDevices];
         int device = 0;
         if (int s = current_device(&device)) return s;
+        if (int s = allow_shared(prepare_plain_kernel<CPL>, PlainPlan<CPL>::kBytes, done, device)) return s;
         prepare_plain_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
                                     PlainPlan<CPL>::kBytes, stream>>>(
             static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride, tokens);
