@@ -5,16 +5,16 @@
 //
 // The kernels are bound by instruction issue, not by HBM, so the layout is chosen to issue few
 // instructions per element:
-//   * one persistent block per SM; inside it several independent row workers (32 threads per
+//   * one persistent block per SM; inside it several independent row workers (64 threads per
 //     2048 columns each, synchronised by named barriers) so that one worker's loads overlap the
 //     others' arithmetic, and what every row needs is staged in shared memory once per block
 //     (the norm and modulation vectors; the 64 Ki-entry table of bf16(sigmoid(f16)));
-//   * a thread owns 32 positions of each of two 256-element Hadamard groups - the index bits
-//     0-2, 4 and 6 - so each radix-4 stage after the first keeps one of its two digits in the
-//     thread and needs one shuffle per two outputs (1.5 shuffles per element, not 4.5);
-//   * the two groups of a thread travel as the halves of packed f32x2 registers through the
-//     butterflies, the adaLN arithmetic and the scaling (add/sub/mul.rn.f32x2 are the IEEE
-//     operations of their lanes), which halves the arithmetic issue slots.
+//   * a thread owns 32 positions of one 256-element Hadamard group - the index bits 0-2, 4 and
+//     6 - so each radix-4 stage after the first keeps one of its two digits in the thread and
+//     needs one shuffle per two outputs (1.5 shuffles per element, not 4.5);
+//   * the two values of index bit 6 travel as the halves of packed f32x2 registers through the
+//     first three stages, the adaLN arithmetic and the scaling (add/sub/mul.rn.f32x2 are the
+//     IEEE operations of their lanes), which halves those issue slots.
 // Every f32 step is a single round-to-nearest operation in the order the reference writes, so
 // the bits match the CPU statement; the sum of squares is still taken over the reference's
 // own thread layout (thread l of 256 owns the 8-element chunks j*256 + l).
@@ -27,14 +27,14 @@ namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kSmemLimit = 232448;       // opt-in dynamic shared memory of one sm_100 block
-constexpr int kWideThreads = 576;        // block size limit of the f32 prologues (96 registers)
-constexpr int kPlainThreads = 768;       // of the f16 prologue, which keeps its row packed
+constexpr int kWideThreads = 1024;       // block size limit of the f32 prologues
+constexpr int kPlainThreads = 1024;      // of the f16 prologue
 
 template <int CPL, int MAX_THREADS>
 struct Geometry {
     static constexpr int kWidth = 2048 * CPL;
     static constexpr int kChunks = kWidth / 8;          // 16-byte chunks of 8 elements
-    static constexpr int kWorkerThreads = 32 * CPL;     // eight lanes per pair of groups
+    static constexpr int kWorkerThreads = 64 * CPL;     // eight lanes per group
     static constexpr int kFit = MAX_THREADS / kWorkerThreads;
     static constexpr int kWorkers = kFit < 1 ? 1 : (kFit > 15 ? 15 : kFit);
     static constexpr int kBlockThreads = kWorkers * kWorkerThreads;
@@ -61,8 +61,8 @@ __device__ __forceinline__ void copy_async16(void *shared_dst, const void *globa
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// Two f32 values in one 64-bit register pair: `a` belongs to the first group of the thread,
-// `b` to the second (or, in the adaLN arithmetic, to the next column).
+// Two f32 values in one 64-bit register pair: `a` is the position with index bit 6 clear, `b`
+// the one with it set (or, in the adaLN arithmetic, the next column).
 struct F2 {
     float a, b;
 };
@@ -164,18 +164,15 @@ __device__ __forceinline__ uint32_t pack_s8x4(int x0, int x1, int x2, int x3) {
 // ---------------------------------------------------------------- thread layout
 // Chunk c of a group (its index bits 3-7) is split as c = c0 + 2 c1 + 4 c2 + 8 c3 + 16 c4:
 // c0, c2, c4 are lane bits 0-2, c1 and c3 live in the thread, lane bits 3-4 and the warp pick
-// the pair of groups.  `first_chunk` is the chunk of the first group at c1 = c3 = 0; the
-// second group lies 32 chunks further on.
+// the group.  `first_chunk` is the thread's chunk at c1 = c3 = 0.
 struct Layout {
     int first_chunk;
-    __device__ __forceinline__ int chunk(int group, int c3, int c1) const {
-        return first_chunk + 32 * group + 8 * c3 + 2 * c1;
-    }
+    __device__ __forceinline__ int chunk(int c3, int c1) const { return first_chunk + 8 * c3 + 2 * c1; }
 };
 
 __device__ __forceinline__ Layout make_layout(int warp_in_worker, int lane) {
-    const int pair = warp_in_worker * 4 + (lane >> 3);
-    return Layout{pair * 64 + (lane & 1) + 4 * ((lane >> 1) & 1) + 16 * ((lane >> 2) & 1)};
+    const int group = warp_in_worker * 4 + (lane >> 3);
+    return Layout{group * 32 + (lane & 1) + 4 * ((lane >> 1) & 1) + 16 * ((lane >> 2) & 1)};
 }
 
 // Row staging in shared memory: chunk i sits in slot i ^ 2*(bit 4 of i), so that the eight
@@ -186,7 +183,7 @@ __device__ __forceinline__ int staged_slot(int chunk) { return chunk ^ (((chunk 
 __device__ __forceinline__ int vector_slot(int unit) { return unit ^ ((unit >> 3) & 1) ^ (((unit >> 5) & 1) << 2); }
 
 // ---------------------------------------------------------------- Hadamard, f32 (norm, gated)
-// One radix-4 butterfly on both groups (kernels/prepare_norm_i8.loom:194-201).
+// One radix-4 butterfly on both halves (kernels/prepare_norm_i8.loom:194-201).
 __device__ __forceinline__ void butterfly2(F2 &e0, F2 &e1, F2 &e2, F2 &e3) {
     F2 s01 = add2(e0, e1), s23 = add2(e2, e3);
     F2 d01 = sub2(e0, e1), d23 = sub2(e2, e3);
@@ -207,26 +204,30 @@ __device__ __forceinline__ void split_stage(F2 &lo, F2 &hi, int mask) {
     hi = sub2(s, dp);
 }
 
-// The group-256 Hadamard of the thread's two groups, strides 1, 4, 16, 64
-// (kernels/prepare_norm_i8.loom:174-309).  x[c3][c1][e]: position e + 16 c1 + 64 c3 (+ lanes).
-__device__ __forceinline__ void hadamard256(F2 (&x)[2][2][8]) {
+// The last stage (strides 64 | 128): its low digit is the packing dimension itself.
+__device__ __forceinline__ void unpacked_stage(F2 &v, int mask) {
+    float s = __fadd_rn(v.a, v.b), d = __fsub_rn(v.a, v.b);
+    float dp = __shfl_xor_sync(kFull, d, mask);
+    v.a = __fadd_rn(s, dp);
+    v.b = __fsub_rn(s, dp);
+}
+
+// The group-256 Hadamard of the thread's group, strides 1, 4, 16, 64
+// (kernels/prepare_norm_i8.loom:174-309).  x[c1][e]: positions e + 16 c1 (+ lanes), halves c3.
+__device__ __forceinline__ void hadamard256(F2 (&x)[2][8]) {
 #pragma unroll
-    for (int c3 = 0; c3 < 2; c3++)
+    for (int c1 = 0; c1 < 2; c1++) {
+        butterfly2(x[c1][0], x[c1][1], x[c1][2], x[c1][3]);
+        butterfly2(x[c1][4], x[c1][5], x[c1][6], x[c1][7]);
 #pragma unroll
-        for (int c1 = 0; c1 < 2; c1++) {
-            butterfly2(x[c3][c1][0], x[c3][c1][1], x[c3][c1][2], x[c3][c1][3]);
-            butterfly2(x[c3][c1][4], x[c3][c1][5], x[c3][c1][6], x[c3][c1][7]);
+        for (int c = 0; c < 4; c++) split_stage(x[c1][c], x[c1][c + 4], 1);  // strides 4 | 8
+    }
 #pragma unroll
-            for (int c = 0; c < 4; c++) split_stage(x[c3][c1][c], x[c3][c1][c + 4], 1);  // strides 4 | 8
-        }
-#pragma unroll
-    for (int c3 = 0; c3 < 2; c3++)
-#pragma unroll
-        for (int e = 0; e < 8; e++) split_stage(x[c3][0][e], x[c3][1][e], 2);  // strides 16 | 32
+    for (int e = 0; e < 8; e++) split_stage(x[0][e], x[1][e], 2);  // strides 16 | 32
 #pragma unroll
     for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-        for (int e = 0; e < 8; e++) split_stage(x[0][c1][e], x[1][c1][e], 4);  // strides 64 | 128
+        for (int e = 0; e < 8; e++) unpacked_stage(x[c1][e], 4);  // strides 64 | 128
 }
 
 // ---------------------------------------------------------------- absmax and codes
@@ -246,7 +247,7 @@ __device__ __forceinline__ void row_scale(float amax, float rotation, float &s, 
     inv = __fdiv_rn(rotation, s);
 }
 
-// Eight values of each group to eight codes each (:331-372).  max(x, -127) before rounding
+// Eight values of each half to eight codes each (:331-372).  max(x, -127) before rounding
 // equals the clamp after it (-127 is an integer) and sends a NaN to -127 as the reference's
 // maxnum does; the saturating pack clamps at +127.
 __device__ __forceinline__ void store_codes(const F2 (&v)[8], float inv, int8_t *first, int8_t *second) {
@@ -262,30 +263,26 @@ __device__ __forceinline__ void store_codes(const F2 (&v)[8], float inv, int8_t 
 }
 
 // Row absmax over the worker (per-warp maxima in `slots`, double-buffered by the caller),
-// then the codes of the thread's 64 positions and the row scale.
-template <int CPL>
-__device__ __forceinline__ void quantise_f32(F2 (&x)[2][2][8], float *slots, int worker, int warp_in_worker,
+// then the codes of the thread's 32 positions and the row scale.
+template <int WARPS>
+__device__ __forceinline__ void quantise_f32(F2 (&x)[2][8], float *slots, int worker, int warp_in_worker,
                                              int lane, const Layout &layout, int8_t *q_row, float *scale_out) {
     float amax = 0.0f;
 #pragma unroll
-    for (int c3 = 0; c3 < 2; c3++)
+    for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-        for (int c1 = 0; c1 < 2; c1++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) amax = fmaxf(amax, fmaxf(fabsf(x[c3][c1][e].a), fabsf(x[c3][c1][e].b)));
+        for (int e = 0; e < 8; e++) amax = fmaxf(amax, fmaxf(fabsf(x[c1][e].a), fabsf(x[c1][e].b)));
     amax = warp_max(amax);
     if (lane == 0) slots[warp_in_worker] = amax;
-    worker_barrier(worker, 32 * CPL);
+    worker_barrier(worker, 32 * WARPS);
     float m = slots[0];
 #pragma unroll
-    for (int i = 1; i < CPL; i++) m = fmaxf(m, slots[i]);
+    for (int i = 1; i < WARPS; i++) m = fmaxf(m, slots[i]);
     float s, inv;
     row_scale(m, 0.0625f, s, inv);
 #pragma unroll
-    for (int c3 = 0; c3 < 2; c3++)
-#pragma unroll
-        for (int c1 = 0; c1 < 2; c1++)
-            store_codes(x[c3][c1], inv, q_row + 8 * layout.chunk(0, c3, c1), q_row + 8 * layout.chunk(1, c3, c1));
+    for (int c1 = 0; c1 < 2; c1++)
+        store_codes(x[c1], inv, q_row + 8 * layout.chunk(0, c1), q_row + 8 * layout.chunk(1, c1));
     if (warp_in_worker == 0 && lane == 0) *scale_out = s;
 }
 
@@ -304,7 +301,7 @@ template <int CPL>
 struct NormPlan {
     using G = Geometry<CPL, kWideThreads>;
     static constexpr int kRowBytes = 2 * G::kWorkers * G::kWidth * 2;  // two buffers per worker
-    static constexpr int kSmallBytes = G::kWorkers * (8 + 2 * 16) * 4;
+    static constexpr int kSmallBytes = G::kWorkers * (8 + 2 * 32) * 4;
     static constexpr int kVectorBytes = G::kWidth * (4 + 4 + 2);
     static constexpr bool kStaged = kVectorBytes + kRowBytes + kSmallBytes <= kSmemLimit;
     static constexpr int kBytes = (kStaged ? kVectorBytes : 0) + kRowBytes + kSmallBytes;
@@ -336,7 +333,8 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     using G = Geometry<CPL, kWideThreads>;
     using Plan = NormPlan<CPL>;
     constexpr int width = G::kWidth;
-    constexpr int kVirtual = (8 + CPL - 1) / CPL;  // reference waves (of 8) a warp sums
+    constexpr int kWarps = 2 * CPL;                      // of one worker
+    constexpr int kVirtual = (8 + kWarps - 1) / kWarps;  // reference waves (of 8) a warp sums
     extern __shared__ __align__(16) uint8_t smem[];
     float *vec_norm = reinterpret_cast<float *>(smem);
     float *vec_shift = vec_norm + width;
@@ -371,7 +369,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     const Layout layout = make_layout(warp, lane);
     uint4 *row_bufs = row_store + 2 * worker * G::kChunks;
     float *sums = sum_store + worker * 8;
-    float *maxes = max_store + worker * 32;
+    float *maxes = max_store + worker * 64;
     int parity = 0;
 
     // The next row streams into the worker's other buffer (16-byte asynchronous copies, slot-swizzled)
@@ -380,7 +378,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
         const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
         uint4 *dst = row_bufs + buffer * G::kChunks;
 #pragma unroll
-        for (int i = 0; i < 8; i++) copy_async16(dst + staged_slot(t + i * G::kWorkerThreads), src + t + i * G::kWorkerThreads);
+        for (int i = 0; i < 4; i++) copy_async16(dst + staged_slot(t + i * G::kWorkerThreads), src + t + i * G::kWorkerThreads);
         copy_async_commit();
     };
     Rows rows = worker_rows(tokens, worker);
@@ -390,15 +388,15 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     }
     worker_barrier(worker, G::kWorkerThreads);
 
-    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
         const size_t row = rows.next;
         const uint4 *row_buf = row_bufs + (parity ? G::kChunks : 0);
         if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, parity ? 0 : 1);
         // Sum of squares in the reference's layout: its wave v, lane l, step j owns chunk
-        // j*256 + v*32 + l.  A warp of this worker takes the waves warp, warp + CPL, ...
+        // j*256 + v*32 + l.  A warp of this worker takes the waves warp, warp + 2 CPL, ...
 #pragma unroll
         for (int i = 0; i < kVirtual; i++) {
-            const int wave = warp + i * CPL;
+            const int wave = warp + i * kWarps;
             if (wave < 8) {
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -424,14 +422,13 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
         float mean_eps = __fadd_rn(__fdiv_rn(total, static_cast<float>(width)), eps);
         float rinv = __fdiv_rn(1.0f, __fsqrt_rn(mean_eps));
 
-        F2 x[2][2][8];
+        F2 x[2][8];
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+        for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++)
-#pragma unroll
-                for (int group = 0; group < 2; group++) {
-                    const int chunk = layout.chunk(group, c3, c1), col = chunk * 8;
+            for (int c3 = 0; c3 < 2; c3++) {
+                {
+                    const int chunk = layout.chunk(c3, c1), col = chunk * 8;
                     const uint4 packed = row_buf[staged_slot(chunk)];
                     float o[8], ns[8], sh[8];
                     uint32_t m[4];
@@ -460,13 +457,14 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                     adaln_chunk(packed, rinv, ns, m, sh, o);
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        if (group == 0) x[c3][c1][e].a = o[e];
-                        else x[c3][c1][e].b = o[e];
+                        if (c3 == 0) x[c1][e].a = o[e];
+                        else x[c1][e].b = o[e];
                     }
                 }
+            }
         hadamard256(x);
         copy_async_wait();  // the next row: published by the barrier inside quantise_f32
-        quantise_f32<CPL>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
+        quantise_f32<kWarps>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
     }
 }
 
@@ -504,7 +502,7 @@ constexpr int kTableBytes = 65536 * 2;
 template <int CPL>
 struct GatedPlan {
     using G = Geometry<CPL, kWideThreads>;
-    static constexpr int kBytes = kTableBytes + G::kWorkers * 2 * 16 * 4 + 16;
+    static constexpr int kBytes = kTableBytes + G::kWorkers * 2 * 32 * 4 + 16;
 };
 
 template <int CPL>
@@ -514,10 +512,11 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
                      size_t gate_stride, size_t tokens) {
     using G = Geometry<CPL, kWideThreads>;
     constexpr int width = G::kWidth;
+    constexpr int kWarps = 2 * CPL;
     extern __shared__ __align__(16) uint8_t smem[];
     uint16_t *table = reinterpret_cast<uint16_t *>(smem);
     float *max_store = reinterpret_cast<float *>(smem + kTableBytes);
-    int *ready = reinterpret_cast<int *>(max_store + G::kWorkers * 32);
+    int *ready = reinterpret_cast<int *>(max_store + G::kWorkers * 64);
 
     if (threadIdx.x == 0) {
         int flag;
@@ -537,50 +536,46 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
-    float *maxes = max_store + worker * 32;
+    float *maxes = max_store + worker * 64;
     int parity = 0;
 
-    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
         const size_t row = rows.next;
         const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * width);
         const uint4 *g_src = reinterpret_cast<const uint4 *>(gate + row * gate_stride);
-        uint4 a_raw[2][2][2], g_raw[2][2][2];
+        uint4 a_raw[2][2], g_raw[2][2];
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+        for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++)
+            for (int c3 = 0; c3 < 2; c3++) {
+                a_raw[c1][c3] = load_stream(a_src + layout.chunk(c3, c1));
+                g_raw[c1][c3] = load_stream(g_src + layout.chunk(c3, c1));
+            }
+        F2 x[2][8];
 #pragma unroll
-                for (int group = 0; group < 2; group++) {
-                    a_raw[c3][c1][group] = load_stream(a_src + layout.chunk(group, c3, c1));
-                    g_raw[c3][c1][group] = load_stream(g_src + layout.chunk(group, c3, c1));
-                }
-        F2 x[2][2][8];
+        for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+            for (int c3 = 0; c3 < 2; c3++) {
+                const uint4 &ar = a_raw[c1][c3], &gr = g_raw[c1][c3];
+                const uint32_t aw[4] = {ar.x, ar.y, ar.z, ar.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++)
-#pragma unroll
-                for (int group = 0; group < 2; group++) {
-                    const uint4 &ar = a_raw[c3][c1][group], &gr = g_raw[c3][c1][group];
-                    const uint32_t aw[4] = {ar.x, ar.y, ar.z, ar.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        // kernels/prepare_gated_i8.loom:94-106
-                        const uint32_t a = pack_bf16x2(unpack_f16x2(aw[k]));
-                        const uint32_t g = static_cast<uint32_t>(table[gw[k] & 0xffffu]) |
-                                           (static_cast<uint32_t>(table[gw[k] >> 16]) << 16);
-                        F2 o = bf_round2(product_bf16x2(a, g));
-                        if (group == 0) {
-                            x[c3][c1][2 * k].a = o.a;
-                            x[c3][c1][2 * k + 1].a = o.b;
-                        } else {
-                            x[c3][c1][2 * k].b = o.a;
-                            x[c3][c1][2 * k + 1].b = o.b;
-                        }
+                for (int k = 0; k < 4; k++) {
+                    // kernels/prepare_gated_i8.loom:94-106
+                    const uint32_t a = pack_bf16x2(unpack_f16x2(aw[k]));
+                    const uint32_t g = static_cast<uint32_t>(table[gw[k] & 0xffffu]) |
+                                       (static_cast<uint32_t>(table[gw[k] >> 16]) << 16);
+                    F2 o = bf_round2(product_bf16x2(a, g));
+                    if (c3 == 0) {
+                        x[c1][2 * k].a = o.a;
+                        x[c1][2 * k + 1].a = o.b;
+                    } else {
+                        x[c1][2 * k].b = o.a;
+                        x[c1][2 * k + 1].b = o.b;
                     }
                 }
+            }
         hadamard256(x);
-        quantise_f32<CPL>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
+        quantise_f32<kWarps>(x, maxes + parity, worker, warp, lane, layout, q + row * out_stride, q_scale + row);
     }
 }
 
@@ -597,11 +592,18 @@ __device__ __forceinline__ void split_stage_f16(uint32_t &lo, uint32_t &hi, int 
     hi = pack_f16x2(sub2(s, dp));
 }
 
+__device__ __forceinline__ void unpacked_stage_f16(uint32_t &w, int mask) {
+    F2 v = unpack_quarter_f16x2(w);
+    float s = __fadd_rn(v.a, v.b), d = __fsub_rn(v.a, v.b);
+    float dp = __shfl_xor_sync(kFull, d, mask);
+    w = pack_f16x2(F2{__fadd_rn(s, dp), __fsub_rn(s, dp)});
+}
+
 template <int CPL>
 struct PlainPlan {
     using G = Geometry<CPL, kPlainThreads>;
-    static constexpr int kStageBytes = 2 * 8 * 16 * G::kBlockThreads;  // two rows of eight chunks per thread
-    static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * 16 * 4;
+    static constexpr int kStageBytes = 2 * 4 * 16 * G::kBlockThreads;  // two rows of four chunks per thread
+    static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * 32 * 4;
 };
 
 template <int CPL>
@@ -610,91 +612,84 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
                      size_t out_stride, size_t tokens) {
     using G = Geometry<CPL, kPlainThreads>;
     constexpr int width = G::kWidth;
+    constexpr int kWarps = 2 * CPL;
     extern __shared__ __align__(16) uint8_t smem[];
     uint4 *stage = reinterpret_cast<uint4 *>(smem);
     float *max_store = reinterpret_cast<float *>(smem + PlainPlan<CPL>::kStageBytes);
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
-    float *maxes = max_store + worker * 32;
+    float *maxes = max_store + worker * 64;
     int parity = 0;
 
-    // Each thread streams its own eight chunks of the next row into shared memory while it works
-    // on this one: slot (buffer, piece) of thread x is stage[(buffer*8 + piece) * threads + x].
+    // Each thread streams its own four chunks of the next row into shared memory while it works
+    // on this one: slot (buffer, piece) of thread x is stage[(buffer*4 + piece) * threads + x].
     auto fetch = [&](size_t row, int buffer) {
         const uint4 *src = reinterpret_cast<const uint4 *>(h + row * width);
 #pragma unroll
-        for (int piece = 0; piece < 8; piece++)
-            copy_async16(stage + (buffer * 8 + piece) * G::kBlockThreads + threadIdx.x,
-                         src + layout.chunk(piece & 1, piece >> 2, (piece >> 1) & 1));
+        for (int piece = 0; piece < 4; piece++)
+            copy_async16(stage + (buffer * 4 + piece) * G::kBlockThreads + threadIdx.x,
+                         src + layout.chunk(piece & 1, piece >> 1));
         copy_async_commit();
     };
     Rows rows = worker_rows(tokens, worker);
     if (rows.next < rows.end) fetch(rows.next, 0);
 
-    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 16) {
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
         const size_t row = rows.next;
         const int buffer = parity ? 1 : 0;
         copy_async_wait();
-        uint32_t x[2][2][8];
+        uint32_t x[2][8];  // f16x2 words: low half c3 = 0, high half c3 = 1
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+        for (int c1 = 0; c1 < 2; c1++) {
+            const uint4 ra = stage[(buffer * 4 + 2 * c1) * G::kBlockThreads + threadIdx.x];
+            const uint4 rb = stage[(buffer * 4 + 2 * c1 + 1) * G::kBlockThreads + threadIdx.x];
+            const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
+            F2 e[8];
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++) {
-                const uint4 ra = stage[(buffer * 8 + 4 * c3 + 2 * c1) * G::kBlockThreads + threadIdx.x];
-                const uint4 rb = stage[(buffer * 8 + 4 * c3 + 2 * c1 + 1) * G::kBlockThreads + threadIdx.x];
-                const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
-                F2 e[8];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const F2 fa = unpack_quarter_f16x2(aw[k]), fb = unpack_quarter_f16x2(bw[k]);
-                    e[2 * k] = F2{fa.a, fb.a};
-                    e[2 * k + 1] = F2{fa.b, fb.b};
-                }
-                butterfly2(e[0], e[1], e[2], e[3]);
-                butterfly2(e[4], e[5], e[6], e[7]);
-#pragma unroll
-                for (int k = 0; k < 8; k++) x[c3][c1][k] = pack_f16x2(e[k]);
-#pragma unroll
-                for (int c = 0; c < 4; c++) split_stage_f16(x[c3][c1][c], x[c3][c1][c + 4], 1);
+            for (int k = 0; k < 4; k++) {
+                const F2 fa = unpack_quarter_f16x2(aw[k]), fb = unpack_quarter_f16x2(bw[k]);
+                e[2 * k] = F2{fa.a, fb.a};
+                e[2 * k + 1] = F2{fa.b, fb.b};
             }
+            butterfly2(e[0], e[1], e[2], e[3]);
+            butterfly2(e[4], e[5], e[6], e[7]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) x[c1][k] = pack_f16x2(e[k]);
+#pragma unroll
+            for (int c = 0; c < 4; c++) split_stage_f16(x[c1][c], x[c1][c + 4], 1);
+        }
         if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, buffer ^ 1);
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) split_stage_f16(x[c3][0][e], x[c3][1][e], 2);
+        for (int e = 0; e < 8; e++) split_stage_f16(x[0][e], x[1][e], 2);
 #pragma unroll
         for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-            for (int e = 0; e < 8; e++) split_stage_f16(x[0][c1][e], x[1][c1][e], 4);
+            for (int e = 0; e < 8; e++) unpacked_stage_f16(x[c1][e], 4);
 
         // absmax on the packed halves (exact: a maximum of f16 values), then as in the f32 prologues.
         __half2 packed_max = __float2half2_rn(0.0f);
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+        for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++)
-#pragma unroll
-                for (int e = 0; e < 8; e++)
-                    packed_max = __hmax2(packed_max, __habs2(*reinterpret_cast<const __half2 *>(&x[c3][c1][e])));
+            for (int e = 0; e < 8; e++)
+                packed_max = __hmax2(packed_max, __habs2(*reinterpret_cast<const __half2 *>(&x[c1][e])));
         float amax = warp_max(fmaxf(__low2float(packed_max), __high2float(packed_max)));
         if (lane == 0) maxes[parity + warp] = amax;
         worker_barrier(worker, G::kWorkerThreads);
         float m = maxes[parity];
 #pragma unroll
-        for (int i = 1; i < CPL; i++) m = fmaxf(m, maxes[parity + i]);
+        for (int i = 1; i < kWarps; i++) m = fmaxf(m, maxes[parity + i]);
         float s, inv;
         row_scale(m, 16.0f, s, inv);
         int8_t *q_row = q + row * out_stride;
 #pragma unroll
-        for (int c3 = 0; c3 < 2; c3++)
+        for (int c1 = 0; c1 < 2; c1++) {
+            F2 v[8];
 #pragma unroll
-            for (int c1 = 0; c1 < 2; c1++) {
-                F2 v[8];
-#pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = unpack_f16x2(x[c3][c1][e]);
-                store_codes(v, inv, q_row + 8 * layout.chunk(0, c3, c1), q_row + 8 * layout.chunk(1, c3, c1));
-            }
+            for (int e = 0; e < 8; e++) v[e] = unpack_f16x2(x[c1][e]);
+            store_codes(v, inv, q_row + 8 * layout.chunk(0, c1), q_row + 8 * layout.chunk(1, c1));
+        }
         if (warp == 0 && lane == 0) q_scale[row] = s;
     }
 }
