@@ -302,7 +302,7 @@ def run_b200(args, dims, config):
             per_launch_ms = stage_ms[label] / layers
             kernels[label] = {"m": m, "n": n, "k": kk, "ms_per_launch": per_launch_ms,
                               "tops": 2.0 * m * n * kk / (per_launch_ms * 1e-3) / 1e12}
-        for label in ("prepare", "prepare gated", "prepare swiglu", "attention stand-in"):
+        for label in ("prepare", "prepare gated", "prepare swiglu"):
             kernels[label] = {"ms_per_forward": stage_ms.get(label, 0.0)}
         gu = kernels["gemm gate|up + swiglu"]
         int8_peak = 2.0 * peaks["bf16_tflops_sustained"]

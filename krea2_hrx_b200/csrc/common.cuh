@@ -37,6 +37,9 @@ int prepare_gemm_device();
 // Defined with the attention kernel: the same for it, and its share of the device status word.
 int prepare_attention_device();
 int take_attention_status(int *value);
+// Defined with the prologues: prepare_gated_i8 whose attention rows have a pitch of their own (in elements).
+int prepare_gated_pitched(cudaStream_t stream, size_t tokens, const void *attn, size_t attn_stride, const void *gate,
+                          void *q, float *q_scale, size_t width, size_t out_stride, size_t gate_stride);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

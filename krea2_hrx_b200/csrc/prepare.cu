@@ -509,9 +509,8 @@ template <int CPL>
 __global__ void __launch_bounds__(Geometry<CPL, kWideThreads>::kBlockThreads, 1)
 prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restrict__ gate,
                      int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride,
-                     size_t gate_stride, size_t tokens) {
+                     size_t gate_stride, size_t attn_stride, size_t tokens) {
     using G = Geometry<CPL, kWideThreads>;
-    constexpr int width = G::kWidth;
     constexpr int kWarps = 2 * CPL;
     extern __shared__ __align__(16) uint8_t smem[];
     uint16_t *table = reinterpret_cast<uint16_t *>(smem);
@@ -541,7 +540,7 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
 
     for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
         const size_t row = rows.next;
-        const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * width);
+        const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * attn_stride);
         const uint4 *g_src = reinterpret_cast<const uint4 *>(gate + row * gate_stride);
         uint4 a_raw[2][2], g_raw[2][2];
 #pragma unroll
@@ -799,7 +798,7 @@ int ensure_sigmoid_table(cudaStream_t stream, int device) {
 template <int CPL>
 struct LaunchGated {
     static int run(cudaStream_t stream, size_t tokens, const void *attn, const void *gate, void *q,
-                   float *q_scale, size_t out_stride, size_t gate_stride) {
+                   float *q_scale, size_t out_stride, size_t gate_stride, size_t attn_stride) {
         using G = Geometry<CPL, kWideThreads>;
         static std::atomic<bool> done[kMaxDevices];
         int device = 0;
@@ -809,7 +808,7 @@ struct LaunchGated {
         prepare_gated_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
                                     GatedPlan<CPL>::kBytes, stream>>>(
             static_cast<const uint16_t *>(attn), static_cast<const uint16_t *>(gate), static_cast<int8_t *>(q),
-            q_scale, out_stride, gate_stride, tokens);
+            q_scale, out_stride, gate_stride, attn_stride, tokens);
         return finish_launch("prepare_gated_i8");
     }
 };
@@ -901,19 +900,30 @@ extern "C" int krea2_prepare_norm_i8(krea2_stream stream, size_t tokens, const v
                                       mod_shift, q, q_scale, out_stride, eps);
 }
 
-extern "C" int krea2_prepare_gated_i8(krea2_stream stream, size_t tokens, const void *attn, const void *gate,
-                                      void *q, float *q_scale, size_t width, size_t out_stride,
-                                      size_t gate_stride) {
-    clear_error();
+// prepare_gated_i8 with a row pitch on the attention input as well (the C entry point below has
+// the reference's signature, whose attention rows are dense).
+int krea2::prepare_gated_pitched(cudaStream_t stream, size_t tokens, const void *attn, size_t attn_stride,
+                                 const void *gate, void *q, float *q_scale, size_t width, size_t out_stride,
+                                 size_t gate_stride) {
     if (int status = check_prologue("prepare_gated_i8", tokens, width, out_stride)) return status;
     KREA2_REQUIRE(gate_stride >= 256 && gate_stride <= 65536 && gate_stride % 256 == 0 && gate_stride >= width,
                   "prepare_gated_i8: gate_stride %zu must be a multiple of 256 in 256..65536 and at least the width",
                   gate_stride);
+    KREA2_REQUIRE(attn_stride >= width && attn_stride % 8 == 0,
+                  "prepare_gated_i8: attention pitch %zu must be a multiple of 8 and at least the width", attn_stride);
     KREA2_REQUIRE(attn && gate && q && q_scale, "prepare_gated_i8: null buffer");
     KREA2_REQUIRE(aligned16(attn) && aligned16(gate) && aligned16(q),
                   "prepare_gated_i8: buffers must be 16-byte aligned");
-    return dispatch_width<LaunchGated>(width, static_cast<cudaStream_t>(stream), tokens, attn, gate, q, q_scale,
-                                       out_stride, gate_stride);
+    return dispatch_width<LaunchGated>(width, stream, tokens, attn, gate, q, q_scale, out_stride, gate_stride,
+                                       attn_stride);
+}
+
+extern "C" int krea2_prepare_gated_i8(krea2_stream stream, size_t tokens, const void *attn, const void *gate,
+                                      void *q, float *q_scale, size_t width, size_t out_stride,
+                                      size_t gate_stride) {
+    clear_error();
+    return prepare_gated_pitched(static_cast<cudaStream_t>(stream), tokens, attn, width, gate, q, q_scale, width,
+                                 out_stride, gate_stride);
 }
 
 extern "C" int krea2_prepare_plain_i8(krea2_stream stream, size_t tokens, const void *h, void *q, float *q_scale,

@@ -249,13 +249,14 @@ int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *
         KREA2_STEP("f16 attention",
                    krea2_attention_gqa_lds_f16_wmma(stream, t, d.kv_heads, s->q, s->k, s->v_transposed, s->attn_gu, hidden,
                                                     kv_width, hidden, s->capacity, 0.08838834764831845f))
+        KREA2_STEP("prepare gated", krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q,
+                                                           s->a_s, hidden, ph, s->qkvg))
     } else {
-        if ((status = mark("attention stand-in"))) return status;
-        KREA2_CUDA(cudaMemcpy2DAsync(s->attn_gu, hidden * 2, s->fused, s->qkvg * 2, hidden * 2, t,
-                                     cudaMemcpyDeviceToDevice, stream));
+        // W8A8-only mode: the q columns of the fused buffer stand in for the attention output and
+        // are read where they lie, through the row pitch of that buffer.
+        KREA2_STEP("prepare gated", prepare_gated_pitched(stream, t, s->fused, s->qkvg, s->fused + s->gate_offset * 2, s->a_q,
+                                                          s->a_s, hidden, ph, s->qkvg))
     }
-    KREA2_STEP("prepare gated", krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q, s->a_s,
-                                                       hidden, ph, s->qkvg))
     KREA2_STEP("gemm wo + residual", krea2_gemm_i8_resid_256(stream, t, s->a_q, w.wo_q, w.wo_s, s->a_s, s->x,
                                                              mods + 2 * hidden, hidden, ph, hidden, group))
     KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q,
@@ -538,7 +539,7 @@ extern "C" size_t krea2_session_stage_profile(const krea2_session *s, const char
     return n;
 }
 extern "C" size_t krea2_session_launches_per_forward(const krea2_session *s) {
-    // eleven kernels per block with attention; eight without (the stand-in copy is not a kernel of this library)
+    // eleven kernels per block with attention; eight without
     return s ? s->layers * (s->attention ? 11 : 8) : 0;
 }
 

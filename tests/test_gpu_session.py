@@ -156,7 +156,7 @@ def test_profiled_forward_reports_the_reference_stage_labels(small):
     s.set_attention(False)
     s.set_profile(True)
     s.run(stream, profiled, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
-    assert "attention stand-in" in dict(s.stage_profile()) and s.launches_per_forward() == 3 * 8
+    assert "f16 attention" not in dict(s.stage_profile()) and s.launches_per_forward() == 3 * 8
     assert s.set_profile(False) is True
     s.close()
 
