@@ -119,6 +119,28 @@ int krea2_rope_qknorm_f16(krea2_stream stream, size_t tokens, const void *qkv, c
  * they are written as zero. */
 int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x, void *out, size_t width, size_t row_capacity);
 
+/* ---------------------------------------------------------------- around the block chain
+ * The pointwise kernels of the sampler loop and its sigma schedule (src/pipeline/mod.rs:340-357). */
+
+/* kernels/native/modulation.loom (launched at src/models/graph.rs:405-425): y[i] = bf16(x[i % xsize] +
+ * tables[i]) as f32, i < count - the f32 [layers][6][width] table a session reads, from this
+ * timestep's bf16 vector x [xsize] and the bf16 block tables [count]. */
+int krea2_modulation(krea2_stream stream, size_t count, const void *x, const void *tables, float *y, size_t xsize);
+
+/* kernels/native/euler.loom (src/ops/mod.rs:373-390): sample = bf16(sample + bf16(bf16(delta) * velocity))
+ * in place; sample, velocity bf16 [count]. */
+int krea2_euler(krea2_stream stream, size_t count, float delta, void *sample, const void *velocity);
+
+/* kernels/native/guidance.loom (src/ops/mod.rs:392-410): cond = bf16(cond + bf16(scale * bf16(cond - uncond)))
+ * in place; cond, uncond bf16 [count]. */
+int krea2_guidance(krea2_stream stream, size_t count, float scale, void *cond, const void *uncond);
+
+/* src/pipeline/schedule.rs:11-35: the shift of an image with that many tokens; the sigma at `step` of
+ * `steps` (zero at step == steps); the sigma a step lands on when the run ends after step `last`. */
+double krea2_schedule_dynamic_mu(size_t image_tokens);
+float krea2_schedule_sigma(size_t step, size_t steps, double mu);
+float krea2_schedule_next_sigma(size_t step, size_t last, size_t steps, double mu);
+
 /* kernels/attention_gqa_lds_f16_wmma.loom:18-41 (and the _q32 sibling, the same function on
  * 32-row groups).  q f16 [tokens][q_stride], k f16 [tokens][kv_stride], v_transposed f16
  * [kv_stride][token_capacity] with finite (zero) headroom past `tokens`, out f16
@@ -269,6 +291,45 @@ int krea2_weights_download(const krea2_weights *weights, const char *name, void 
                            krea2_stream stream);
 void krea2_weights_retain(krea2_weights *weights);
 void krea2_weights_release(krea2_weights *weights);
+
+/* ---------------------------------------------------------------- checkpoint ingestion
+ * A ComfyUI int8 ConvRot checkpoint (.safetensors) mapped read-only and indexed under the transformer's
+ * own tensor names (src/checkpoint/file.rs), the device layout derived from it (src/checkpoint/plan.rs)
+ * and the upload (src/session/weights.rs).  Everything up to krea2_weights_load_checkpoint is host work:
+ * a malformed file is refused without touching a device. */
+typedef struct krea2_checkpoint krea2_checkpoint;
+
+/* Plan::span (plan.rs:23-43).  segments = checkpoint row ranges that fill it in order (0 for the spans
+ * assembled on the host: gathered channel scales, bf16 norm vectors); file_bytes = bytes before padding. */
+typedef struct krea2_span_info {
+    size_t device_offset, device_bytes, rows, row_bytes, device_row_bytes, segments, file_bytes;
+} krea2_span_info;
+
+/* Checkpoint::open (file.rs:72-90): the extension must be .safetensors; an unreadable or inconsistent
+ * file is KREA2_INVALID_ARGUMENT with a message that starts "cannot read <path>".  A namespace every
+ * tensor shares in front of "blocks.0.attn.wq.weight" is removed (file.rs:39-57). */
+int krea2_checkpoint_open(const char *path, krea2_checkpoint **out);
+void krea2_checkpoint_close(krea2_checkpoint *checkpoint);
+int krea2_checkpoint_has(const krea2_checkpoint *checkpoint, const char *name);
+/* Blocks counted by their attention weights (file.rs:119-125). */
+size_t krea2_checkpoint_block_count(const krea2_checkpoint *checkpoint);
+/* Tensor names in sorted order; returns the count, fills at most `capacity` pointers. */
+size_t krea2_checkpoint_names(const krea2_checkpoint *checkpoint, const char **names, size_t capacity);
+/* Checkpoint::get (file.rs:103-109): dtype string, shape, raw little-endian bytes inside the mapping. */
+int krea2_checkpoint_tensor(const krea2_checkpoint *checkpoint, const char *name, const char **dtype,
+                            const size_t **shape, size_t *rank, const void **bytes, size_t *byte_count);
+/* Plan::for_checkpoint (plan.rs:85-144); the plan is derived on first use and kept. */
+int krea2_checkpoint_plan(krea2_checkpoint *checkpoint, size_t *total_bytes, size_t *layers, size_t *span_count);
+int krea2_checkpoint_span_name(krea2_checkpoint *checkpoint, size_t index, const char **name);
+int krea2_checkpoint_span(krea2_checkpoint *checkpoint, const char *name, krea2_span_info *info);
+int krea2_checkpoint_segment(krea2_checkpoint *checkpoint, const char *span, size_t index, const char **tensor,
+                             size_t *row_begin, size_t *row_end);
+/* The span as it lies on the device (rows at the device pitch, padding zero), written to host memory. */
+int krea2_checkpoint_assemble(krea2_checkpoint *checkpoint, const char *span, void *host_bytes, size_t bytes);
+/* The block shape the file's tensors declare. */
+int krea2_checkpoint_dims(krea2_checkpoint *checkpoint, krea2_dims *dims, size_t *layers);
+/* Weights::load (src/session/weights.rs:40-98): allocates the block on the current device and fills it. */
+int krea2_weights_load_checkpoint(krea2_checkpoint *checkpoint, krea2_stream stream, krea2_weights **out);
 
 /* Session::with_weights (src/session/mod.rs:265-276): buffers at shape::capacity(tokens)
  * rows, zero-filled headroom, bound to `stream` (calls on another stream are refused,

@@ -107,7 +107,55 @@ inline void launch_1d(krea2_stream stream, const char *name, const std::vector<k
                       std::size_t elements) {
     launch(stream, name, config, scalars, bindings, (elements + 255) / 256, 1, 256);
 }
+// Ops::euler_step and Ops::guidance (:373-410), Models::modulation (src/models/graph.rs:405-425).
+inline void euler_step(krea2_stream stream, void *sample, const void *velocity, std::size_t elements, float delta) {
+    check(krea2_euler(stream, elements, delta, sample, velocity));
+}
+inline void guidance(krea2_stream stream, void *cond, const void *uncond, std::size_t elements, float scale) {
+    check(krea2_guidance(stream, elements, scale, cond, uncond));
+}
+inline void modulation(krea2_stream stream, const void *vector, std::size_t vector_elements, const void *tables,
+                       float *out, std::size_t elements) {
+    check(krea2_modulation(stream, elements, vector, tables, out, vector_elements));
+}
 }  // namespace ops
+
+// pipeline::schedule (src/pipeline/schedule.rs).
+namespace schedule {
+inline double dynamic_mu(std::size_t image_tokens) { return krea2_schedule_dynamic_mu(image_tokens); }
+inline float sigma(std::size_t step, std::size_t steps, double mu) { return krea2_schedule_sigma(step, steps, mu); }
+inline float next_sigma(std::size_t step, std::size_t last, std::size_t steps, double mu) {
+    return krea2_schedule_next_sigma(step, last, steps, mu);
+}
+}  // namespace schedule
+
+// checkpoint::Checkpoint (src/checkpoint/file.rs) and its Plan (src/checkpoint/plan.rs).
+namespace checkpoint {
+class Checkpoint {
+public:
+    explicit Checkpoint(const std::string &path) { check(krea2_checkpoint_open(path.c_str(), &handle_)); }
+    Checkpoint(const Checkpoint &) = delete;
+    Checkpoint &operator=(const Checkpoint &) = delete;
+    ~Checkpoint() { krea2_checkpoint_close(handle_); }
+    bool has(const std::string &name) const { return krea2_checkpoint_has(handle_, name.c_str()) != 0; }
+    std::size_t block_count() const { return krea2_checkpoint_block_count(handle_); }
+    // Plan::span: where a named operand goes on the device and which rows fill it.
+    krea2_span_info span(const std::string &name) const {
+        krea2_span_info info{};
+        check(krea2_checkpoint_span(handle_, name.c_str(), &info));
+        return info;
+    }
+    std::size_t total_bytes() const {
+        std::size_t total = 0;
+        check(krea2_checkpoint_plan(handle_, &total, nullptr, nullptr));
+        return total;
+    }
+    krea2_checkpoint *raw() const { return handle_; }
+
+private:
+    krea2_checkpoint *handle_ = nullptr;
+};
+}  // namespace checkpoint
 
 namespace session {
 constexpr std::size_t HIDDEN = 6144, KV_HEADS = 12, HEAD_DIM = 128, INTER = 16384;       // src/session/mod.rs:35-41
@@ -117,6 +165,10 @@ constexpr std::size_t GATE_OFFSET = HIDDEN + 2 * KV_HEADS * HEAD_DIM;           
 class Weights {
 public:
     Weights(const krea2_dims &dims, std::size_t layers) { check(krea2_weights_create(&dims, layers, &handle_)); }
+    // Weights::load (src/session/weights.rs:40-44).
+    Weights(const checkpoint::Checkpoint &file, krea2_stream stream) {
+        check(krea2_weights_load_checkpoint(file.raw(), stream, &handle_));
+    }
     Weights(const Weights &other) : handle_(other.handle_) { krea2_weights_retain(handle_); }  // Arc<Weights>
     Weights &operator=(const Weights &) = delete;
     ~Weights() { krea2_weights_release(handle_); }

@@ -54,6 +54,11 @@ class Shard(ctypes.Structure):
                 ("offset", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p), ("epoch_base", c_void_p)]
 
 
+class SpanInfo(ctypes.Structure):
+    _fields_ = [(name, c_size_t) for name in ("device_offset", "device_bytes", "rows", "row_bytes",
+                                               "device_row_bytes", "segments", "file_bytes")]
+
+
 class Dims(ctypes.Structure):
     _fields_ = [("hidden", c_size_t), ("kv_heads", c_size_t), ("head_dim", c_size_t), ("inter", c_size_t)]
 
@@ -80,6 +85,12 @@ SIGNATURES = {
     "krea2_rope_qknorm_f16": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
     "krea2_v_transpose": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_size_t]),
+    "krea2_modulation": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t]),
+    "krea2_euler": (c_int, [c_void_p, c_size_t, c_float, c_void_p, c_void_p]),
+    "krea2_guidance": (c_int, [c_void_p, c_size_t, c_float, c_void_p, c_void_p]),
+    "krea2_schedule_dynamic_mu": (c_double, [c_size_t]),
+    "krea2_schedule_sigma": (c_float, [c_size_t, c_size_t, c_double]),
+    "krea2_schedule_next_sigma": (c_float, [c_size_t, c_size_t, c_size_t, c_double]),
     "krea2_attention_gqa_lds_f16_wmma": (c_int, [c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
     "krea2_attention_gqa_lds_f16_wmma_q32": (c_int, [c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
     "krea2_gemm_i8_sharded": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
@@ -115,6 +126,21 @@ SIGNATURES = {
     "krea2_weights_download": (c_int, [c_void_p, c_char_p, c_void_p, c_size_t, c_void_p]),
     "krea2_weights_retain": (None, [c_void_p]),
     "krea2_weights_release": (None, [c_void_p]),
+    "krea2_checkpoint_open": (c_int, [c_char_p, POINTER(c_void_p)]),
+    "krea2_checkpoint_close": (None, [c_void_p]),
+    "krea2_checkpoint_has": (c_int, [c_void_p, c_char_p]),
+    "krea2_checkpoint_block_count": (c_size_t, [c_void_p]),
+    "krea2_checkpoint_names": (c_size_t, [c_void_p, POINTER(c_char_p), c_size_t]),
+    "krea2_checkpoint_tensor": (c_int, [c_void_p, c_char_p, POINTER(c_char_p), POINTER(POINTER(c_size_t)),
+                                        POINTER(c_size_t), POINTER(c_void_p), POINTER(c_size_t)]),
+    "krea2_checkpoint_plan": (c_int, [c_void_p, POINTER(c_size_t), POINTER(c_size_t), POINTER(c_size_t)]),
+    "krea2_checkpoint_span_name": (c_int, [c_void_p, c_size_t, POINTER(c_char_p)]),
+    "krea2_checkpoint_span": (c_int, [c_void_p, c_char_p, POINTER(SpanInfo)]),
+    "krea2_checkpoint_segment": (c_int, [c_void_p, c_char_p, c_size_t, POINTER(c_char_p), POINTER(c_size_t),
+                                         POINTER(c_size_t)]),
+    "krea2_checkpoint_assemble": (c_int, [c_void_p, c_char_p, c_void_p, c_size_t]),
+    "krea2_checkpoint_dims": (c_int, [c_void_p, POINTER(Dims), POINTER(c_size_t)]),
+    "krea2_weights_load_checkpoint": (c_int, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "krea2_session_create": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, POINTER(c_void_p)]),
     "krea2_session_destroy": (None, [c_void_p]),
     "krea2_session_tokens": (c_size_t, [c_void_p]),

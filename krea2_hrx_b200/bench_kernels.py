@@ -165,10 +165,32 @@ def run_attention(kind, m, dims, iters, warmup, flush):
             "gflop": gflop, "tflops": gflop / ms}
 
 
+def run_sampler(kind, m, dims, iters, warmup, flush):
+    """The pointwise kernels around the chain: `euler` and `guidance` over m x hidden bf16 elements (inputs
+    larger than L2 at the default m), `modulation` over the [28][6][hidden] tables."""
+    h = dims["hidden"]
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    if kind == "modulation":
+        count = 28 * 6 * h
+        vector = torch.randn(6 * h, generator=gen, device="cuda").to(torch.bfloat16)
+        tables = torch.randn(count, generator=gen, device="cuda").to(torch.bfloat16)
+        out = torch.empty(count, dtype=torch.float32, device="cuda")
+        ms = time_launches(lambda: ops.modulation(vector, tables, out), iters, warmup, flush)
+        nbytes = count * 6
+    else:
+        count = m * h
+        a = torch.randn(count, generator=gen, device="cuda").to(torch.bfloat16)
+        b = torch.randn(count, generator=gen, device="cuda").to(torch.bfloat16)
+        fn = (lambda: ops.euler_step(a, b, -0.1234)) if kind == "euler" else (lambda: ops.guidance(a, b, 3.5))
+        ms = time_launches(fn, iters, warmup, flush)
+        nbytes = count * 6  # two bf16 reads and one bf16 write per element
+    return {"kernel": kind, "elements": count, "ms": ms, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", default="all",
-                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, gemms, prologues or all "
+                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, euler, guidance, modulation, gemms, prologues or all "
                              "(comma separated)")
     parser.add_argument("--m", default="4608", help="rows, comma separated; 'reference' = the reference's bench list")
     parser.add_argument("--dims", default="reference", choices=sorted(DIMS))
@@ -185,7 +207,8 @@ def main():
     for kind in kinds:
         for m in rows:
             runner = run_prologue if kind in ("norm", "gated", "plain") else \
-                run_attention if kind in ("rope", "vt", "attention") else run_gemm
+                run_attention if kind in ("rope", "vt", "attention") else \
+                run_sampler if kind in ("euler", "guidance", "modulation") else run_gemm
             result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
             result["dims"] = args.dims
             print(json.dumps(result), flush=True)

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkrea2_b200.so")
-SOURCES = ["api.cu", "prepare.cu", "gemm_i8.cu", "session.cu", "quantized.cu", "attention.cu"]
+SOURCES = ["api.cu", "prepare.cu", "gemm_i8.cu", "session.cu", "quantized.cu", "attention.cu", "sampler.cu", "checkpoint.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-O2,-Wall", "--expt-relaxed-constexpr",

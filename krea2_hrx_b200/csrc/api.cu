@@ -197,5 +197,26 @@ extern "C" int krea2_launch(krea2_stream stream, const char *name, const krea2_c
         if (int s = check_bindings(name, b, binding_count, 2, min_bytes)) return s;
         return krea2_lora_transport(stream, rows, b[0].ptr, b[1].ptr, static_cast<int>(reverse));
     }
+    // The pointwise kernels of the sampler loop, launched by Ops::launch_1d over `rows` elements.  Their
+    // float scalar (Scalars::float, src/kernels/mod.rs:125-134) travels as the `fvalue` of a config entry.
+    const bool euler = std::strcmp(name, "euler") == 0, guide = std::strcmp(name, "guidance") == 0;
+    if (euler || guide) {
+        const char *key = euler ? "delta" : "scale";
+        const krea2_config_entry *scalar = config.find(key);
+        if (!scalar) return fail(KREA2_INVALID_ARGUMENT, "%s: float scalar '%s' is missing", name, key);
+        if (int s = check_geometry(name, grid_x, grid_y, threads, (rows + 255) / 256, 1, 256)) return s;
+        const size_t min_bytes[2] = {rows * 2, rows * 2};
+        if (int s = check_bindings(name, b, binding_count, 2, min_bytes)) return s;
+        return euler ? krea2_euler(stream, rows, scalar->fvalue, b[0].ptr, b[1].ptr)
+                     : krea2_guidance(stream, rows, scalar->fvalue, b[0].ptr, b[1].ptr);
+    }
+    if (std::strcmp(name, "modulation") == 0) {
+        uint64_t xsize = 0;
+        if (int s = need(config, name, "xsize", &xsize)) return s;
+        if (int s = check_geometry(name, grid_x, grid_y, threads, (rows + 255) / 256, 1, 256)) return s;
+        const size_t min_bytes[3] = {static_cast<size_t>(xsize) * 2, rows * 2, rows * 4};
+        if (int s = check_bindings(name, b, binding_count, 3, min_bytes)) return s;
+        return krea2_modulation(stream, rows, b[0].ptr, b[1].ptr, static_cast<float *>(b[2].ptr), xsize);
+    }
     return fail(KREA2_INVALID_ARGUMENT, "no kernel named %s", name);
 }

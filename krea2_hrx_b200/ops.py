@@ -30,12 +30,17 @@ def _bytes(t: torch.Tensor) -> int:
     return t.numel() * t.element_size()
 
 
+FLOAT_SCALARS = {"euler": "delta", "guidance": "scale"}
+
+
 class Ops:
     """The generic dispatcher: kernel by name, config by key, scalars, buffers in binding order."""
 
     def launch(self, stream, name: str, config: kernels.Config, scalars: kernels.Scalars,
                bindings: Sequence[torch.Tensor], grid_x: int, grid_y: int, threads: int) -> None:
         kernels.grid(name, grid_x, grid_y)
+        if scalars.floats and name in FLOAT_SCALARS:  # Scalars::float: the C ABI carries it as a config float
+            config = {**config, FLOAT_SCALARS[name]: float(scalars.floats[0])}
         entries = (ConfigEntry * max(1, len(config)))()
         for i, (key, value) in enumerate(config.items()):
             entries[i].key = key.encode()
@@ -179,3 +184,27 @@ def attention_gqa(tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride
     fn = lib().krea2_attention_gqa_lds_f16_wmma_q32 if q32 else lib().krea2_attention_gqa_lds_f16_wmma
     check(fn(_stream_ptr(stream), tokens, kv_heads, _ptr(q), _ptr(k), _ptr(v_transposed), _ptr(out), q_stride, kv_stride,
              out_stride, token_capacity, scale))
+
+
+# ------------------------------------------------------------------ around the block chain
+def modulation(vector, tables, out, stream=None):
+    """Models::modulation (src/models/graph.rs:405-425): `out` f32 = bf16(vector[i % len] + tables[i])."""
+    if out.numel() != tables.numel():
+        raise InvalidArgument("modulation dimensions")
+    check(lib().krea2_modulation(_stream_ptr(stream), tables.numel(), _ptr(vector), _ptr(tables), _ptr(out),
+                                 vector.numel()))
+
+
+def euler_step(sample, velocity, delta, stream=None):
+    """Ops::euler_step (src/ops/mod.rs:373-390): `sample += delta * velocity` in place with the sampler's
+    bf16 rounding at the delta, the product and the sum."""
+    if tuple(sample.shape) != tuple(velocity.shape):
+        raise InvalidArgument("scheduler tensor dimensions")
+    check(lib().krea2_euler(_stream_ptr(stream), sample.numel(), float(delta), _ptr(sample), _ptr(velocity)))
+
+
+def guidance(cond, uncond, scale, stream=None):
+    """Ops::guidance (src/ops/mod.rs:392-410): `cond += scale * (cond - uncond)` in place, bf16 at each step."""
+    if tuple(cond.shape) != tuple(uncond.shape):
+        raise InvalidArgument("guidance tensor dimensions")
+    check(lib().krea2_guidance(_stream_ptr(stream), cond.numel(), float(scale), _ptr(cond), _ptr(uncond)))

@@ -48,6 +48,22 @@ class Weights:
         check(lib().krea2_weights_create(ctypes.byref(c_dims), layers, ctypes.byref(handle)))
         self._handle = handle
 
+    @classmethod
+    def load(cls, path, stream=None) -> "Weights":
+        """Weights::load (src/session/weights.rs:40-44): reads the checkpoint, derives the layout, uploads it."""
+        from .checkpoint import Checkpoint
+        checkpoint = Checkpoint(path)
+        try:
+            (hidden, kv_heads, head_dim, inter), layers = checkpoint.dims()
+            handle = ctypes.c_void_p()
+            check(lib().krea2_weights_load_checkpoint(checkpoint._handle, _stream_ptr(stream), ctypes.byref(handle)))
+        finally:
+            checkpoint.close()
+        self = cls.__new__(cls)
+        self.dims, self.layers = ModelDims(hidden=hidden, kv_heads=kv_heads, head_dim=head_dim, inter=inter), layers
+        self._handle = handle
+        return self
+
     @staticmethod
     def plan_bytes(dims: ModelDims, layers: int) -> int:
         n = ctypes.c_size_t()

@@ -39,6 +39,12 @@ def lib() -> ctypes.CDLL:
         _lib.oracle_exp.restype = ctypes.c_float
         _lib.oracle_exp.argtypes = [ctypes.c_float]
         _lib.oracle_threads.restype = ctypes.c_int
+        _lib.oracle_dynamic_mu.restype = ctypes.c_double
+        _lib.oracle_dynamic_mu.argtypes = [ctypes.c_size_t]
+        _lib.oracle_sigma.restype = ctypes.c_float
+        _lib.oracle_sigma.argtypes = [ctypes.c_size_t, ctypes.c_size_t, ctypes.c_double]
+        _lib.oracle_next_sigma.restype = ctypes.c_float
+        _lib.oracle_next_sigma.argtypes = [ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_double]
     return _lib
 
 
@@ -217,3 +223,40 @@ def attention_gqa(q, k, v, q_heads, kv_heads, scale):
     lib().oracle_attention_gqa(_sz(queries), _sz(tokens), _sz(q_heads), _sz(kv_heads), _p(q), _p(k), _p(v), _p(out),
                                ctypes.c_double(scale))
     return out
+
+
+# ------------------------------------------------------------------ the outer step
+def modulation(x, tables):
+    """x: bf16 bits [xsize]; tables: bf16 bits [count] -> f32 [count] (bf16-rounded sums)."""
+    x, tables = np.ascontiguousarray(x, dtype=np.uint16), np.ascontiguousarray(tables, dtype=np.uint16)
+    y = np.empty(tables.size, dtype=np.float32)
+    lib().oracle_modulation(_sz(tables.size), _p(x), _p(tables), _p(y), _sz(x.size))
+    return y.reshape(tables.shape)
+
+
+def euler(sample, velocity, delta):
+    """Returns the updated bf16 sample (the input array is not modified)."""
+    out = np.array(sample, dtype=np.uint16, copy=True)
+    velocity = np.ascontiguousarray(velocity, dtype=np.uint16)
+    lib().oracle_euler(_sz(out.size), ctypes.c_float(delta), _p(out), _p(velocity))
+    return out
+
+
+def guidance(cond, uncond, scale):
+    """Returns the updated bf16 conditional velocity (the input array is not modified)."""
+    out = np.array(cond, dtype=np.uint16, copy=True)
+    uncond = np.ascontiguousarray(uncond, dtype=np.uint16)
+    lib().oracle_guidance(_sz(out.size), ctypes.c_float(scale), _p(out), _p(uncond))
+    return out
+
+
+def dynamic_mu(image_tokens: int) -> float:
+    return float(lib().oracle_dynamic_mu(image_tokens))
+
+
+def sigma(step: int, steps: int, mu: float) -> float:
+    return float(lib().oracle_sigma(step, steps, mu))
+
+
+def next_sigma(step: int, last: int, steps: int, mu: float) -> float:
+    return float(lib().oracle_next_sigma(step, last, steps, mu))

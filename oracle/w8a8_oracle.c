@@ -458,3 +458,51 @@ void oracle_attention_gqa(size_t queries, size_t tokens, size_t q_heads, size_t 
             free(scores);
         }
 }
+
+/* ---------------------------------------------------------------- the outer step
+ * The three pointwise kernels around the block chain and the sigma schedule.  All
+ * pinned: the reference tests state euler and guidance exactly (tests/arithmetic.rs:38-84)
+ * and hold the schedule to recorded scheduler bits (tests/schedule.rs). */
+
+/* kernels/native/modulation.loom:30-43: y[i] = bf16(x[i % xsize] + tables[i]) widened to f32. */
+void oracle_modulation(size_t count, const uint16_t *x, const uint16_t *tables, float *y, size_t xsize) {
+    for (size_t i = 0; i < count; i++) y[i] = bf(bf16_to_f32(x[i % xsize]) + bf16_to_f32(tables[i]));
+}
+
+/* kernels/native/euler.loom:28-41: sample = bf16(sample + bf16(bf16(delta) * velocity)). */
+void oracle_euler(size_t count, float delta, uint16_t *sample, const uint16_t *velocity) {
+    const float dt = bf(delta);
+    for (size_t i = 0; i < count; i++) {
+        float product = bf(dt * bf16_to_f32(velocity[i]));
+        sample[i] = f32_to_bf16(bf16_to_f32(sample[i]) + product);
+    }
+}
+
+/* kernels/native/guidance.loom:28-43: cond = bf16(cond + bf16(scale * bf16(cond - uncond))). */
+void oracle_guidance(size_t count, float scale, uint16_t *cond, const uint16_t *uncond) {
+    for (size_t i = 0; i < count; i++) {
+        float c = bf16_to_f32(cond[i]);
+        float difference = bf(c - bf16_to_f32(uncond[i]));
+        cond[i] = f32_to_bf16(c + bf(scale * difference));
+    }
+}
+
+/* src/pipeline/schedule.rs:11-14 */
+double oracle_dynamic_mu(size_t image_tokens) {
+    double slope = (1.15 - 0.5) / (6400.0 - 256.0);
+    return (double)image_tokens * slope + (0.5 - slope * 256.0);
+}
+
+/* src/pipeline/schedule.rs:17-27: the linspace value in f32, exp(mu) in double then f32. */
+float oracle_sigma(size_t step, size_t steps, double mu) {
+    if (step == steps) return 0.0f;
+    float raw = (float)(1.0 - (double)step / (double)steps);
+    float shift = (float)exp(mu);
+    float offset = 1.0f / raw - 1.0f;
+    return shift / (shift + offset);
+}
+
+/* src/pipeline/schedule.rs:33-35 */
+float oracle_next_sigma(size_t step, size_t last, size_t steps, double mu) {
+    return step + 1 >= last ? 0.0f : oracle_sigma(step + 1, steps, mu);
+}
