@@ -574,6 +574,11 @@ extern "C" int krea2_session_run(krea2_session *s, krea2_stream stream, uint16_t
         if (int status = upload_rope(s, host_cos, host_sin)) return status;
         if (s->profile) {
             if (int status = run_profiled(s, first_block, count)) return status;
+        } else if (first_block == 0 && count == s->layers) {
+            // The whole chain: the recorded graph, as run_device replays it (same launches, fewer gaps).
+            if (!s->graph)
+                if (int status = record_graph(s)) return status;
+            KREA2_CUDA(cudaGraphLaunch(s->graph, s->stream));
         } else {
             for (size_t i = first_block; i < first_block + count; i++)
                 if (int status = run_block(s, s->stream, i, nullptr)) return status;
