@@ -100,14 +100,25 @@ v_transpose_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out, u
 }
 
 // ---------------------------------------------------------------- attention
-constexpr int kTile = 128;            // query rows per CTA, keys per step, channels per head
+// One CTA owns two query tiles of 128 rows (softmax groups A and B, four warps each) and walks the
+// keys in tiles of 128.  Per group and key tile: S = Q K^T (tcgen05, f32 in tensor memory), the
+// group's warps read their rows, keep a running maximum and sum, write P = 2^(S - max) as f16 back
+// into the first 64 columns of the same S region, and O += P V takes P straight from tensor
+// memory, so P never crosses shared memory (whose bandwidth a 128 x 128 f16 product with both
+// operands in shared memory already saturates) and a K or V tile is loaded once for both groups.
+// The tensor pipe runs one thread's products in issue order and a commit covers everything
+// issued before it; that is what orders P V of tile j before the S of tile j + 1 that overwrites
+// P, and P V of tile j - 1 before the softmax of tile j rescales O.  While one group is in its
+// softmax the pipe works for the other.
+constexpr int kTile = 128;            // query rows per group, keys per step, channels per head
 constexpr int kSubtileBytes = 16384;  // [128 rows][64 f16]: one 128-byte swizzled column block
 constexpr int kOperandBytes = 2 * kSubtileBytes;
-constexpr int kAttnThreads = 352;     // warps 0-3 and 4-7: two softmax groups; 8 Q+K loads; 9 MMA; 10 V loads
+constexpr int kAttnThreads = 352;     // warps 0-3 and 4-7: the two softmax groups; 8 Q+K loads; 9 MMA; 10 V loads
 constexpr int kGroupWarps = 4;
 constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9, kTmaWarpV = 10;
+constexpr int kKvStages = 2;
 constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
-constexpr int kAttnSmemBytes = 7 * kOperandBytes + 1024 + 256 + 1024;  // Q, K x2, V x2, P x2, barriers, merge
+constexpr int kAttnSmemBytes = (2 + 2 * kKvStages) * kOperandBytes + 1024 + 1024;  // Q x2, K, V stages, barriers
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint64_t timer_ns() {
@@ -137,22 +148,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// One non-blocking look at a barrier phase (the MMA thread polls several barriers in turn).
-__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
 __device__ int g_attention_status = 0;  // folded into krea2_device_status by take_attention_status
 constexpr int kAttentionTimedOut = 32;
+// Bounded: after two seconds the CTA's abort flag and the device status word are raised and every
+// role falls through to the end of the kernel.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = timer_ns();
@@ -176,6 +175,7 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem] B[smem]
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t accumulate) {
     asm volatile(
@@ -187,11 +187,24 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint6
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= A[tmem] B[smem]: A is M rows (lanes) of f16 pairs, one K = 16 step per eight columns.
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
 __device__ __forceinline__ void tmem_wait_load() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Issues the load of 32 columns without waiting for it (tmem_wait_load completes all loads issued so far).
 __device__ __forceinline__ void tmem_load_32_async(uint32_t address, float *r) {
     uint32_t *u = reinterpret_cast<uint32_t *>(r);
@@ -209,8 +222,8 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, float (&r)[32]) {
     tmem_load_32_async(address, r);
     tmem_wait_load();
 }
-__device__ __forceinline__ void tmem_store_32(uint32_t address, const float (&r)[32]) {
-    const uint32_t *u = reinterpret_cast<const uint32_t *>(r);
+// Issues the store of 32 columns (tmem_wait_store completes all stores issued so far).
+__device__ __forceinline__ void tmem_store_32_async(uint32_t address, const uint32_t *u) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -220,7 +233,10 @@ __device__ __forceinline__ void tmem_store_32(uint32_t address, const float (&r)
         "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]),
         "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t address, const float (&r)[32]) {
+    tmem_store_32_async(address, reinterpret_cast<const uint32_t *>(r));
+    tmem_wait_store();
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -242,15 +258,24 @@ struct AttnArgs {
     uint16_t *out;
 };
 
-// One 128 x 128 x 128 product from two 64-wide K-major subtiles per operand: 8 instructions of K = 16.
-__device__ __forceinline__ void issue_product(uint32_t tmem_d, uint32_t a_addr, uint32_t b_addr, bool accumulate) {
+// S = Q K^T: one 128 x 128 x 128 product from two 64-wide K-major subtiles per operand, 8 instructions of K = 16.
+__device__ __forceinline__ void issue_scores(uint32_t tmem_d, uint32_t q_addr, uint32_t k_addr) {
 #pragma unroll
     for (int sub = 0; sub < 2; sub++) {
-        const uint64_t a_desc = smem_descriptor(a_addr + sub * kSubtileBytes);
-        const uint64_t b_desc = smem_descriptor(b_addr + sub * kSubtileBytes);
+        const uint64_t a_desc = smem_descriptor(q_addr + sub * kSubtileBytes);
+        const uint64_t b_desc = smem_descriptor(k_addr + sub * kSubtileBytes);
+#pragma unroll
+        for (int k = 0; k < 4; k++) umma_f16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, kIdescF16, (sub != 0 || k != 0) ? 1u : 0u);
+    }
+}
+// O (+)= P V with P in tensor memory (eight columns per 16 keys) and V^T in shared memory.
+__device__ __forceinline__ void issue_values(uint32_t tmem_d, uint32_t tmem_p, uint32_t v_addr, bool accumulate) {
+#pragma unroll
+    for (int sub = 0; sub < 2; sub++) {
+        const uint64_t b_desc = smem_descriptor(v_addr + sub * kSubtileBytes);
 #pragma unroll
         for (int k = 0; k < 4; k++)
-            umma_f16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, kIdescF16, (accumulate || sub != 0 || k != 0) ? 1u : 0u);
+            umma_f16_tmem_a(tmem_d, tmem_p + (sub * 4 + k) * 8, b_desc + 2 * k, kIdescF16, (accumulate || sub != 0 || k != 0) ? 1u : 0u);
     }
 }
 
@@ -259,30 +284,28 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *q_smem = smem, *k_smem = smem + kOperandBytes, *v_smem = smem + 3 * kOperandBytes;
-    uint8_t *p_smem = smem + 5 * kOperandBytes;  // one P tile per softmax group
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 7 * kOperandBytes);
-    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
-    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *p_empty = bars + 15, *o_done = bars + 17;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
+    uint8_t *q_smem = smem, *k_smem = smem + 2 * kOperandBytes, *v_smem = k_smem + kKvStages * kOperandBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(v_smem + kKvStages * kOperandBytes);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = k_full + kKvStages, *v_full = k_empty + kKvStages;
+    uint64_t *v_empty = v_full + kKvStages, *s_full = v_empty + kKvStages, *p_full = s_full + 2, *o_done = p_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_done + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *merge = reinterpret_cast<float *>(smem + 7 * kOperandBytes + 256);  // group 1's (reference, sum) per row
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q0 = blockIdx.x * kTile, head = blockIdx.y, kv_head = head / g.q_heads_per_kv;
+    const uint32_t q0 = blockIdx.x * 2 * kTile, head = blockIdx.y, kv_head = head / g.q_heads_per_kv;
     const uint32_t tiles = (g.tokens + kTile - 1) / kTile;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < kKvStages; s++) {
             mbar_init(k_full + s, 1);
             mbar_init(k_empty + s, 1);
             mbar_init(v_full + s, 1);
             mbar_init(v_empty + s, 1);
-            mbar_init(s_full + s, 1);
-            mbar_init(s_empty + s, kGroupWarps);
-            mbar_init(p_full + s, kGroupWarps);
-            mbar_init(p_empty + s, 1);
+        }
+        for (int grp = 0; grp < 2; grp++) {
+            mbar_init(s_full + grp, 1);
+            mbar_init(p_full + grp, kGroupWarps);
         }
         mbar_init(o_done, 1);
         *abort_flag = 0;
@@ -298,15 +321,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;  // S of group 0 and 1 at columns 0 and 128, their O at 256 and 384
+    const uint32_t tmem_base = *tmem_slot;  // S (then P) of groups A and B at columns 0 and 128, their O at 256 and 384
 
     if (warp == kTmaWarpAttn) {
         if (lane == 0) {
-            mbar_expect_tx(q_full, kOperandBytes);
-            tma_load_2d(q_smem, &map_q, q_full, static_cast<int>(head * kTile), static_cast<int>(q0));
-            tma_load_2d(q_smem + kSubtileBytes, &map_q, q_full, static_cast<int>(head * kTile + 64), static_cast<int>(q0));
+            mbar_expect_tx(q_full, 2 * kOperandBytes);
+#pragma unroll
+            for (int grp = 0; grp < 2; grp++) {
+                uint8_t *dst = q_smem + grp * kOperandBytes;
+                const int row = static_cast<int>(q0 + grp * kTile);
+                tma_load_2d(dst, &map_q, q_full, static_cast<int>(head * kTile), row);
+                tma_load_2d(dst + kSubtileBytes, &map_q, q_full, static_cast<int>(head * kTile + 64), row);
+            }
             for (uint32_t j = 0; j < tiles; j++) {
-                const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+                const uint32_t s = j % kKvStages, phase = (j / kKvStages) & 1u;
                 const int key0 = static_cast<int>(j * kTile);
                 if (!mbar_wait(k_empty + s, phase ^ 1u, abort_flag)) break;
                 mbar_expect_tx(k_full + s, kOperandBytes);
@@ -314,18 +342,18 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tma_load_2d(k_dst, &map_k, k_full + s, static_cast<int>(kv_head * kTile), key0);
                 tma_load_2d(k_dst + kSubtileBytes, &map_k, k_full + s, static_cast<int>(kv_head * kTile + 64), key0);
             }
-            if (*abort_flag) {
+            if (*abort_flag) {  // let copies in flight land before the block's shared memory is given back
                 const uint64_t start = timer_ns();
                 while (timer_ns() - start < 200000ull) {
                 }
             }
         }
     } else if (warp == kTmaWarpV) {
-        // V tiles have a producer of their own: a V stage frees up only after its P V product, much
-        // later than the K stage of the same tile, and must not hold back the next K load.
+        // V tiles have a producer of their own: a V stage frees up only after its P V products, later
+        // than the K stage of the same tile, and must not hold back the next K load.
         if (lane == 0) {
             for (uint32_t j = 0; j < tiles; j++) {
-                const uint32_t s = j & 1u, phase = (j >> 1) & 1u;
+                const uint32_t s = j % kKvStages, phase = (j / kKvStages) & 1u;
                 const int key0 = static_cast<int>(j * kTile);
                 if (!mbar_wait(v_empty + s, phase ^ 1u, abort_flag)) break;
                 mbar_expect_tx(v_full + s, kOperandBytes);
@@ -341,77 +369,55 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     } else if (warp == kMmaWarpAttn) {
         if (lane == 0) {
-            bool alive = mbar_wait(q_full, 0, abort_flag);
-            tc_fence_after();
-            const uint32_t q_addr = smem_u32(q_smem);
-            // Key tile j belongs to softmax group j & 1, which owns K/V stage, S buffer, P tile and O
-            // accumulator j & 1, so the two groups' products are independent streams.  The issuing
-            // thread polls both and issues whatever is ready: S of a group's next tile as soon as its S
-            // buffer has been read out, P V of a tile as soon as its P is written.
-            uint32_t s_next[2] = {0u, 1u}, pv_next[2] = {0u, 1u};
-            uint64_t idle_since = 0;
-            uint32_t idle_polls = 0;
-            while (alive) {
-                bool progressed = false, pending = false;
+            bool alive = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full, 0, abort_flag);
+            if (alive) {
+                tc_fence_after();
 #pragma unroll
                 for (uint32_t grp = 0; grp < 2; grp++) {
-                    if (s_next[grp] < tiles) {
-                        pending = true;
-                        const uint32_t parity = (s_next[grp] >> 1) & 1u;
-                        if (mbar_test(k_full + grp, parity) && mbar_test(s_empty + grp, parity ^ 1u)) {
-                            tc_fence_after();
-                            issue_product(tmem_base + grp * kTile, q_addr, smem_u32(k_smem + grp * kOperandBytes), false);
-                            umma_commit(s_full + grp);
-                            umma_commit(k_empty + grp);
-                            s_next[grp] += 2;
-                            progressed = true;
-                        }
-                    }
-                    if (pv_next[grp] < tiles) {
-                        pending = true;
-                        const uint32_t turn = pv_next[grp] >> 1, parity = turn & 1u;
-                        if (pv_next[grp] < s_next[grp] && mbar_test(p_full + grp, parity) && mbar_test(v_full + grp, parity)) {
-                            tc_fence_after();
-                            issue_product(tmem_base + (2 + grp) * kTile, smem_u32(p_smem + grp * kOperandBytes),
-                                          smem_u32(v_smem + grp * kOperandBytes), turn > 0);
-                            umma_commit(p_empty + grp);
-                            umma_commit(v_empty + grp);
-                            pv_next[grp] += 2;
-                            progressed = true;
-                        }
+                    issue_scores(tmem_base + grp * kTile, smem_u32(q_smem + grp * kOperandBytes), smem_u32(k_smem));
+                    umma_commit(s_full + grp);
+                }
+                umma_commit(k_empty);
+            }
+            for (uint32_t j = 0; alive && j < tiles; j++) {
+                const uint32_t s = j % kKvStages, phase = (j / kKvStages) & 1u;
+                const uint32_t next = (j + 1) % kKvStages, next_phase = ((j + 1) / kKvStages) & 1u;
+                const bool more = j + 1 < tiles;
+#pragma unroll
+                for (uint32_t grp = 0; grp < 2; grp++) {
+                    // P V of this tile, then the group's next scores: the pipe keeps them in this order,
+                    // so the scores overwrite P only after it has been read.
+                    alive = alive && mbar_wait(p_full + grp, j & 1u, abort_flag);
+                    if (grp == 0) alive = alive && mbar_wait(v_full + s, phase, abort_flag);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_values(tmem_base + (2 + grp) * kTile, tmem_base + grp * kTile, smem_u32(v_smem + s * kOperandBytes), j > 0);
+                    if (more) {
+                        if (grp == 0) alive = mbar_wait(k_full + next, next_phase, abort_flag);
+                        if (!alive) break;
+                        tc_fence_after();
+                        issue_scores(tmem_base + grp * kTile, smem_u32(q_smem + grp * kOperandBytes),
+                                     smem_u32(k_smem + next * kOperandBytes));
+                        umma_commit(s_full + grp);
                     }
                 }
-                if (!pending) break;
-                if (progressed) {
-                    idle_polls = 0;
-                } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up after two seconds without progress
-                    if (idle_polls == 256u) idle_since = timer_ns();
-                    if (*abort_flag) {
-                        alive = false;
-                    } else if (timer_ns() - idle_since > kAttnWaitLimitNs) {
-                        *abort_flag = 1;
-                        atomicOr(&g_attention_status, kAttentionTimedOut);
-                        alive = false;
-                    }
-                }
+                if (!alive) break;
+                umma_commit(v_empty + s);
+                if (more) umma_commit(k_empty + next);
             }
             if (alive) umma_commit(o_done);
         }
     } else {
-        // Two softmax groups of four warps.  Group `grp` takes key tiles grp, grp + 2, ... and runs its own
-        // online softmax over them (own reference maximum, sum, P tile and O accumulator); the two partial
-        // results are merged at the end.  While one group waits for its scores or reduces a maximum the
-        // other keeps the exponential unit busy.  Warp w reads TMEM lanes 32 * (w % 4) .. + 31.
+        // Softmax group `grp` owns query rows q0 + 128 grp .. + 127: warp w reads TMEM lanes 32 (w % 4) .. + 31,
+        // one row per thread.
         const int grp = warp >> 2, quarter = warp & 3;
         const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t row_in_tile = quarter * 32 + lane;
         const uint32_t s_addr = tmem_base + grp * kTile + lane_bits, o_addr = tmem_base + (2 + grp) * kTile + lane_bits;
-        uint8_t *p_tile = p_smem + grp * kOperandBytes;
         float reference = -INFINITY, sum = 0.0f;  // in units of log2: scores are scaled by scale * log2(e)
         bool alive = true;
-        for (uint32_t j = grp; j < tiles; j += 2) {
-            const uint32_t turn = j >> 1;
-            const bool ready = mbar_wait(s_full + grp, turn & 1u, abort_flag);
+        for (uint32_t j = 0; j < tiles; j++) {
+            const bool ready = mbar_wait(s_full + grp, j & 1u, abort_flag);
             if (!__all_sync(kFull, ready)) {
                 alive = false;
                 break;
@@ -423,10 +429,6 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_load_32_async(s_addr + c * 32, v + c * 32);
             tmem_wait_load();
-            // The scores are in registers: the S buffer can take the group's next tile already.
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + grp);
             if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
 #pragma unroll
                 for (int i = 0; i < kTile; i++)
@@ -444,80 +446,53 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             float alpha = 1.0f;
             const bool move = tile_max > reference + 8.0f;
             if (move) {
-                alpha = fast_exp2(reference - tile_max);  // 0 on the group's first tile
+                alpha = fast_exp2(reference - tile_max);  // 0 on the first tile
                 reference = tile_max;
                 sum *= alpha;
             }
-            // The group's previous P and O must be consumed before P is overwritten and O rescaled.
-            if (turn > 0) {
-                const bool consumed = mbar_wait(p_empty + grp, (turn - 1) & 1u, abort_flag);
-                if (!__all_sync(kFull, consumed)) {
-                    alive = false;
-                    break;
-                }
-                tc_fence_after();
-                if (__any_sync(kFull, move)) {
+            // O holds the products up to tile j - 1 (the commit behind s_full covered them): rescale it in place.
+            if (j > 0 && __any_sync(kFull, move)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
-                        float o[32];
-                        tmem_load_32(o_addr + c * 32, o);
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_load_32(o_addr + c * 32, o);
 #pragma unroll
-                        for (int i = 0; i < 32; i++) o[i] *= alpha;
-                        tmem_store_32(o_addr + c * 32, o);
-                    }
+                    for (int i = 0; i < 32; i++) o[i] *= alpha;
+                    tmem_store_32(o_addr + c * 32, o);
                 }
             }
-            // p = 2^(score - reference), f16, into the K-major swizzled P tile
+            // p = 2^(score - reference) as f16 pairs, back into the first 64 columns of the S region:
+            // key 2c in the low half of column c, which is the A operand layout of the P V product.
             float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t packed[16];
+            for (int c = 0; c < 2; c++) {
+                uint32_t packed[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_exp2(fmaf(v[c * 32 + i], g.scale_log2, -reference));
-                    const float p1 = fast_exp2(fmaf(v[c * 32 + i + 1], g.scale_log2, -reference));
+                for (int i = 0; i < 64; i += 2) {
+                    const float p0 = fast_exp2(fmaf(v[c * 64 + i], g.scale_log2, -reference));
+                    const float p1 = fast_exp2(fmaf(v[c * 64 + i + 1], g.scale_log2, -reference));
                     partial[(i >> 1) & 3] += p0 + p1;
                     const __half2 h = __floats2half2_rn(p0, p1);
                     packed[i / 2] = *reinterpret_cast<const uint32_t *>(&h);
                 }
-                // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key subtile row
-                uint8_t *row_base = p_tile + (c >> 1) * kSubtileBytes + row_in_tile * 128;
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int chunk = (c & 1) * 4 + q;
-                    *reinterpret_cast<uint4 *>(row_base + ((chunk ^ (row_in_tile & 7)) * 16)) =
-                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                }
+                tmem_store_32_async(s_addr + c * 32, packed);
             }
             sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
+            tmem_wait_store();
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + grp);
         }
-        // Merge: group 1 publishes its reference and sum per row; group 0 combines both accumulators.
         const bool finished = alive && mbar_wait(o_done, 0, abort_flag);
-        if (grp == 1) {
-            merge[row_in_tile] = reference;
-            merge[kTile + row_in_tile] = sum;
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
-        if (grp == 0 && __all_sync(kFull, finished)) {
+        if (__all_sync(kFull, finished)) {
             tc_fence_after();
-            const float ref_b = merge[row_in_tile], sum_b = merge[kTile + row_in_tile];
-            const float top = fmaxf(reference, ref_b);
-            const float wa = fast_exp2(reference - top);
-            const float wb = tiles > 1 ? fast_exp2(ref_b - top) : 0.0f;  // with one tile group 1 never ran
-            const float inv = 1.0f / (sum * wa + sum_b * wb);
-            const float fa = wa * inv, fb = wb * inv;
-            const uint32_t row = q0 + row_in_tile;
+            const float inv = 1.0f / sum;
+            const uint32_t row = q0 + grp * kTile + row_in_tile;
             uint16_t *dst = g.out + static_cast<size_t>(row) * g.out_stride + head * kTile;
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
-                float oa[32], ob[32];
-                tmem_load_32_async(tmem_base + 2 * kTile + lane_bits + c * 32, oa);
-                if (tiles > 1) tmem_load_32_async(tmem_base + 3 * kTile + lane_bits + c * 32, ob);
-                tmem_wait_load();
+                float o[32];
+                tmem_load_32(o_addr + c * 32, o);
                 if (row < g.tokens) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
@@ -525,12 +500,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
                             const int e = 8 * q + 2 * i;
-                            float lo = oa[e] * fa, hi = oa[e + 1] * fa;
-                            if (tiles > 1) {
-                                lo = fmaf(ob[e], fb, lo);
-                                hi = fmaf(ob[e + 1], fb, hi);
-                            }
-                            const __half2 h = __floats2half2_rn(lo, hi);
+                            const __half2 h = __floats2half2_rn(o[e] * inv, o[e + 1] * inv);
                             w[i] = *reinterpret_cast<const uint32_t *>(&h);
                         }
                         *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -687,7 +657,7 @@ extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t toke
     args.out_stride = static_cast<uint32_t>(out_stride);
     args.scale_log2 = scale * 1.4426950408889634f;
     args.out = static_cast<uint16_t *>(out);
-    dim3 grid(static_cast<unsigned>((tokens + kTile - 1) / kTile), static_cast<unsigned>(q_stride / 128), 1);
+    dim3 grid(static_cast<unsigned>((tokens + 2 * kTile - 1) / (2 * kTile)), static_cast<unsigned>(q_stride / 128), 1);
     attention_kernel<<<grid, kAttnThreads, kAttnSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, args);
     return launch_check("attention");
 }
