@@ -133,6 +133,34 @@ def test_prologues_are_bit_exact_on_seeded_activations(ops, kind, width):
     np.testing.assert_array_equal(q, want_q)  # includes the untouched 0xA5 padding
 
 
+@pytest.mark.parametrize("kind,tokens,width", [("norm", 4608, 6144), ("gated", 4608, 6144), ("plain", 4608, 16384),
+                                               ("norm", 1043, 6144), ("gated", 1043, 4096), ("plain", 1043, 6144),
+                                               ("norm", 2311, 2048), ("plain", 16397, 2048)])
+def test_prologues_are_bit_exact_over_many_rows_per_worker(ops, kind, tokens, width):
+    """The benchmark's shapes and ragged row counts: every persistent block takes several rows per worker,
+    through the prefetch buffers of both parities and an uneven split of rows over blocks."""
+    rng = np.random.default_rng(tokens + width)
+    stride = width + (64 if width % 8192 == 0 else 0)
+    x = random_rows(rng, tokens, width)
+    x[tokens // 2] = 0.0
+    gate_stride = None
+    if kind == "norm":
+        inputs = (kat.bf16_bits_from_f32(x), (rng.standard_normal(width) * 0.1).astype(np.float32),
+                  (rng.standard_normal(width) * 0.5).astype(np.float32),
+                  (rng.standard_normal(width) * 0.5).astype(np.float32))
+    elif kind == "gated":
+        gate_stride = width + 2 * 1536 + width  # the q|k|v|gate row of a fused buffer
+        gate = np.zeros((tokens, gate_stride), dtype=np.uint16)
+        gate[:, :width] = kat.f16_bits(rng.standard_normal((tokens, width)).astype(np.float32) * 2.0)
+        inputs = (kat.f16_bits(x), gate)
+    else:
+        inputs = (kat.f16_bits(x),)
+    q, qs = run_prologue(ops, kind, inputs, tokens, width, stride, gate_stride)
+    want_q, want_s = oracle_prologue(kind, inputs, width, stride, gate_stride)
+    np.testing.assert_array_equal(qs.view(np.uint32), want_s.view(np.uint32))
+    np.testing.assert_array_equal(q, want_q)
+
+
 def test_gated_prologue_reads_the_gate_through_a_column_view(ops):
     """The session binds the gate as columns GATE_OFFSET.. of the fused buffer
     (src/session/mod.rs:141-144): pitch 15360, view starting 9216 columns in."""
