@@ -37,7 +37,9 @@ int prepare_gemm_device();
 // Defined with the attention kernel: the same for it, and its share of the device status word.
 int prepare_attention_device();
 int take_attention_status(int *value);
-// Defined with the prologues: prepare_gated_i8 whose attention rows have a pitch of their own (in elements).
+// Defined with the prologues: their first-use work, for callers about to capture a stream; and
+// prepare_gated_i8 whose attention rows have a pitch of their own (in elements).
+int prepare_prologue_device(cudaStream_t stream);
 int prepare_gated_pitched(cudaStream_t stream, size_t tokens, const void *attn, size_t attn_stride, const void *gate,
                           void *q, float *q_scale, size_t width, size_t out_stride, size_t gate_stride);
 

@@ -900,6 +900,14 @@ extern "C" int krea2_prepare_norm_i8(krea2_stream stream, size_t tokens, const v
                                       mod_shift, q, q_scale, out_stride, eps);
 }
 
+// First-use work of the gated prologue done ahead of a stream capture: the sigmoid table is filled on
+// `stream` (a fill issued inside a capture would be replayed with the graph every time).
+int krea2::prepare_prologue_device(cudaStream_t stream) {
+    int device = 0;
+    if (int s = current_device(&device)) return s;
+    return ensure_sigmoid_table(stream, device);
+}
+
 // prepare_gated_i8 with a row pitch on the attention input as well (the C entry point below has
 // the reference's signature, whose attention rows are dense).
 int krea2::prepare_gated_pitched(cudaStream_t stream, size_t tokens, const void *attn, size_t attn_stride,

@@ -459,6 +459,7 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     KREA2_REQUIRE(layers <= weights->layers, "the weights hold %zu blocks, %zu were asked for", weights->layers, layers);
     if (int status = prepare_gemm_device()) return status;
     if (int status = prepare_attention_device()) return status;
+    if (int status = prepare_prologue_device(static_cast<cudaStream_t>(stream))) return status;
     std::unique_ptr<krea2_session> s(new krea2_session);
     s->stream = static_cast<cudaStream_t>(stream);
     s->tokens = tokens, s->layers = layers, s->capacity = krea2_shape_capacity(tokens);
