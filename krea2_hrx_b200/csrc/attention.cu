@@ -44,36 +44,52 @@ rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q
     const uint32_t heads_total = q_heads + 2 * kv_heads;
     const float4 cs = __ldg(reinterpret_cast<const float4 *>(cos_table + row * 128 + col));
     const float4 sn = __ldg(reinterpret_cast<const float4 *>(sin_table + row * 128 + col));
-    for (uint32_t head = warp; head < heads_total; head += 8) {
-        const bool is_q = head < q_heads, is_v = head >= q_heads + kv_heads;
-        const uint32_t base = is_q ? head * 128 : k_offset + (head - q_heads) * 128;  // v follows k in the row
-        const uint2 raw = *reinterpret_cast<const uint2 *>(qkv + row * row_stride + base + col);
-        if (is_v) {
-            *reinterpret_cast<uint2 *>(v_out + row * (kv_heads * 128) + (head - q_heads - kv_heads) * 128 + col) = raw;
-            continue;
-        }
-        const __half2 lo = *reinterpret_cast<const __half2 *>(&raw.x), hi = *reinterpret_cast<const __half2 *>(&raw.y);
-        const float v0 = __low2float(lo), v1 = __high2float(lo), v2 = __low2float(hi), v3 = __high2float(hi);
-        float ss = __fadd_rn(__fadd_rn(__fmul_rn(v0, v0), __fmul_rn(v1, v1)), __fadd_rn(__fmul_rn(v2, v2), __fmul_rn(v3, v3)));
+    // A warp's heads are taken three at a time with their loads issued together: one 8-byte load per lane
+    // and head in flight at a time would leave the kernel waiting on memory latency.
+    constexpr int kBatch = 3;
+    for (uint32_t first = warp; first < heads_total; first += 8 * kBatch) {
+        uint2 raws[kBatch];
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(kFull, ss, off));
-        const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, 0.0078125f), eps)));
-        const float4 sc = __ldg(reinterpret_cast<const float4 *>((is_q ? q_scale : k_scale) + col));
-        // x = bf16((h * rinv) * (1 + scale)); out = bf16(x * cos + rot * sin), rot = (-x1, x0, -x3, x2)
-        const float x0 = bf_round(__fmul_rn(__fmul_rn(v0, rinv), __fadd_rn(sc.x, 1.0f)));
-        const float x1 = bf_round(__fmul_rn(__fmul_rn(v1, rinv), __fadd_rn(sc.y, 1.0f)));
-        const float x2 = bf_round(__fmul_rn(__fmul_rn(v2, rinv), __fadd_rn(sc.z, 1.0f)));
-        const float x3 = bf_round(__fmul_rn(__fmul_rn(v3, rinv), __fadd_rn(sc.w, 1.0f)));
-        const float o0 = bf_round(__fadd_rn(__fmul_rn(x0, cs.x), __fmul_rn(__fsub_rn(0.0f, x1), sn.x)));
-        const float o1 = bf_round(__fadd_rn(__fmul_rn(x1, cs.y), __fmul_rn(x0, sn.y)));
-        const float o2 = bf_round(__fadd_rn(__fmul_rn(x2, cs.z), __fmul_rn(__fsub_rn(0.0f, x3), sn.z)));
-        const float o3 = bf_round(__fadd_rn(__fmul_rn(x3, cs.w), __fmul_rn(x2, sn.w)));
-        const __half2 out_lo = __floats2half2_rn(o0, o1), out_hi = __floats2half2_rn(o2, o3);
-        uint2 packed;
-        packed.x = *reinterpret_cast<const uint32_t *>(&out_lo);
-        packed.y = *reinterpret_cast<const uint32_t *>(&out_hi);
-        uint16_t *dst = is_q ? q_out + row * (q_heads * 128) + head * 128 : k_out + row * (kv_heads * 128) + (head - q_heads) * 128;
-        *reinterpret_cast<uint2 *>(dst + col) = packed;
+        for (int b = 0; b < kBatch; b++) {
+            const uint32_t head = first + 8 * b;
+            if (head < heads_total) {
+                const uint32_t base = head < q_heads ? head * 128 : k_offset + (head - q_heads) * 128;  // v follows k in the row
+                raws[b] = *reinterpret_cast<const uint2 *>(qkv + row * row_stride + base + col);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; b++) {
+            const uint32_t head = first + 8 * b;
+            if (head >= heads_total) break;
+            const uint2 raw = raws[b];
+            const bool is_q = head < q_heads, is_v = head >= q_heads + kv_heads;
+            if (is_v) {
+                *reinterpret_cast<uint2 *>(v_out + row * (kv_heads * 128) + (head - q_heads - kv_heads) * 128 + col) = raw;
+                continue;
+            }
+            const __half2 lo = *reinterpret_cast<const __half2 *>(&raw.x), hi = *reinterpret_cast<const __half2 *>(&raw.y);
+            const float v0 = __low2float(lo), v1 = __high2float(lo), v2 = __low2float(hi), v3 = __high2float(hi);
+            float ss = __fadd_rn(__fadd_rn(__fmul_rn(v0, v0), __fmul_rn(v1, v1)), __fadd_rn(__fmul_rn(v2, v2), __fmul_rn(v3, v3)));
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(kFull, ss, off));
+            const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, 0.0078125f), eps)));
+            const float4 sc = __ldg(reinterpret_cast<const float4 *>((is_q ? q_scale : k_scale) + col));
+            // x = bf16((h * rinv) * (1 + scale)); out = bf16(x * cos + rot * sin), rot = (-x1, x0, -x3, x2)
+            const float x0 = bf_round(__fmul_rn(__fmul_rn(v0, rinv), __fadd_rn(sc.x, 1.0f)));
+            const float x1 = bf_round(__fmul_rn(__fmul_rn(v1, rinv), __fadd_rn(sc.y, 1.0f)));
+            const float x2 = bf_round(__fmul_rn(__fmul_rn(v2, rinv), __fadd_rn(sc.z, 1.0f)));
+            const float x3 = bf_round(__fmul_rn(__fmul_rn(v3, rinv), __fadd_rn(sc.w, 1.0f)));
+            const float o0 = bf_round(__fadd_rn(__fmul_rn(x0, cs.x), __fmul_rn(__fsub_rn(0.0f, x1), sn.x)));
+            const float o1 = bf_round(__fadd_rn(__fmul_rn(x1, cs.y), __fmul_rn(x0, sn.y)));
+            const float o2 = bf_round(__fadd_rn(__fmul_rn(x2, cs.z), __fmul_rn(__fsub_rn(0.0f, x3), sn.z)));
+            const float o3 = bf_round(__fadd_rn(__fmul_rn(x3, cs.w), __fmul_rn(x2, sn.w)));
+            const __half2 out_lo = __floats2half2_rn(o0, o1), out_hi = __floats2half2_rn(o2, o3);
+            uint2 packed;
+            packed.x = *reinterpret_cast<const uint32_t *>(&out_lo);
+            packed.y = *reinterpret_cast<const uint32_t *>(&out_hi);
+            uint16_t *dst = is_q ? q_out + row * (q_heads * 128) + head * 128 : k_out + row * (kv_heads * 128) + (head - q_heads) * 128;
+            *reinterpret_cast<uint2 *>(dst + col) = packed;
+        }
     }
 }
 
