@@ -302,8 +302,17 @@ def run_b200(args, dims, config):
             per_launch_ms = stage_ms[label] / layers
             kernels[label] = {"m": m, "n": n, "k": kk, "ms_per_launch": per_launch_ms,
                               "tops": 2.0 * m * n * kk / (per_launch_ms * 1e-3) / 1e12}
-        for label in ("prepare", "prepare gated", "prepare swiglu"):
-            kernels[label] = {"ms_per_forward": stage_ms.get(label, 0.0)}
+        # The prologues against the HBM roofline: algorithmic bytes = one read of each 16-bit input row, one
+        # int8 row and one f32 scale per token (the f32 [K] vectors are amortised over the tokens).
+        hidden, inter = mdims.hidden, mdims.inter
+        prologue_bytes = {"prepare": (2 * layers, tokens * (2 * hidden + hidden + 4)),
+                          "prepare gated": (layers, tokens * (4 * hidden + hidden + 4)),
+                          "prepare swiglu": (layers, tokens * (2 * inter + inter + 4))}
+        for label, (launches, nbytes) in prologue_bytes.items():
+            ms = stage_ms.get(label, 0.0)
+            gbs = nbytes / (ms / launches * 1e-3) / 1e9 if ms > 0 else 0.0
+            kernels[label] = {"ms_per_forward": ms, "launches": launches, "algorithmic_mb_per_launch": nbytes / 1e6,
+                              "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"]}
         gu = kernels["gemm gate|up + swiglu"]
         int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
         roofline = {
