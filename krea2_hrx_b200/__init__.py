@@ -2,19 +2,20 @@
 
 The compute lives in libkrea2_b200.so (CUDA, built from csrc/ by build.py) behind the C ABI of
 include/krea2_b200.h.  The modules here mirror the reference crate's host interface for this path:
-`shape` (kernels::shape), `kernels` (Config, Scalars, Shape), `ops` (Ops::launch, Quantized) and
-`session` (Session, Weights).
+`shape` (kernels::shape), `kernels` (Config, Scalars, Shape), `ops` (Ops::launch, Quantized, the pointwise
+sampler kernels), `session` (Session, Weights), `schedule` (pipeline::schedule), `checkpoint` (Checkpoint, Plan)
+and `parallel` (column-sharded weights over several devices, which the reference does not have).
 """
 from . import kernels, shape  # noqa: F401
 from ._lib import (Cancelled, Error, Internal, InvalidArgument, Poisoned, Runtime, device_status, lib)  # noqa: F401
 
-__all__ = ["kernels", "shape", "ops", "session", "lib", "device_status", "Error", "InvalidArgument", "Cancelled",
+__all__ = ["kernels", "shape", "ops", "session", "schedule", "checkpoint", "parallel", "lib", "device_status", "Error", "InvalidArgument", "Cancelled",
            "Poisoned", "Runtime", "Internal"]
 
 
 def __getattr__(name):
     # ops and session import torch; keep `import krea2_hrx_b200` light for the shape rules.
-    if name in ("ops", "session"):
+    if name in ("ops", "session", "schedule", "checkpoint", "parallel"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)
