@@ -328,6 +328,9 @@ int krea2_checkpoint_segment(krea2_checkpoint *checkpoint, const char *span, siz
 int krea2_checkpoint_assemble(krea2_checkpoint *checkpoint, const char *span, void *host_bytes, size_t bytes);
 /* The block shape the file's tensors declare. */
 int krea2_checkpoint_dims(krea2_checkpoint *checkpoint, krea2_dims *dims, size_t *layers);
+/* Session::validate (src/session/mod.rs:249-261): dimensions, then the checkpoint's header and layout;
+ * no device is touched (tests/constructor.rs). */
+int krea2_session_validate(const char *checkpoint_path, size_t tokens, size_t layers);
 /* Weights::load (src/session/weights.rs:40-98): allocates the block on the current device and fills it. */
 int krea2_weights_load_checkpoint(krea2_checkpoint *checkpoint, krea2_stream stream, krea2_weights **out);
 

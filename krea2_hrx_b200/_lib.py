@@ -140,6 +140,7 @@ SIGNATURES = {
                                          POINTER(c_size_t)]),
     "krea2_checkpoint_assemble": (c_int, [c_void_p, c_char_p, c_void_p, c_size_t]),
     "krea2_checkpoint_dims": (c_int, [c_void_p, POINTER(Dims), POINTER(c_size_t)]),
+    "krea2_session_validate": (c_int, [c_char_p, c_size_t, c_size_t]),
     "krea2_weights_load_checkpoint": (c_int, [c_void_p, c_void_p, POINTER(c_void_p)]),
     "krea2_session_create": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, POINTER(c_void_p)]),
     "krea2_session_destroy": (None, [c_void_p]),

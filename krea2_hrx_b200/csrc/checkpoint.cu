@@ -630,6 +630,18 @@ extern "C" int krea2_checkpoint_dims(krea2_checkpoint *c, krea2_dims *dims, size
     return KREA2_OK;
 }
 
+// Session::validate (src/session/mod.rs:249-261): the session dimensions, then the checkpoint's header
+// and layout.  Host work only: a refusal costs nothing and leaves the driver library unloaded.
+extern "C" int krea2_session_validate(const char *checkpoint_path, size_t tokens, size_t layers) {
+    clear_error();
+    if (int s = krea2_session_validate_dimensions(tokens, layers)) return s;
+    krea2_checkpoint *c = nullptr;
+    if (int s = krea2_checkpoint_open(checkpoint_path, &c)) return s;
+    const int status = build_plan(*c);
+    delete c;
+    return status;
+}
+
 // Weights::load (src/session/weights.rs:40-98): the plan of the file must be the plan the
 // kernels' block shape implies (same names, offsets and extents); then every span is assembled at
 // its device pitch and uploaded.

@@ -98,6 +98,12 @@ class Weights:
             self._handle = None
 
 
+def validate(checkpoint_path, tokens: int, layers: int) -> None:
+    """Session::validate (src/session/mod.rs:249-261): raises InvalidArgument for dimensions this build cannot
+    serve or a checkpoint that cannot be laid out, without touching a device."""
+    check(lib().krea2_session_validate(str(checkpoint_path).encode(), tokens, layers))
+
+
 class Session:
     """session::Session: buffers sized by shape::capacity, bound to its creating stream."""
 

@@ -158,3 +158,68 @@ def test_a_checkpoint_with_inconsistent_blocks_is_refused_before_any_device_work
     plan_oracle.write_safetensors(str(path), wrong)
     with pytest.raises(k.InvalidArgument, match="not int8 ConvRot rows"):
         Checkpoint(path).plan()
+
+
+# ------------------------------------------------------------------ Session::validate (tests/constructor.rs)
+VALIDATE_CHILD = r'''
+import ctypes, json, sys
+lib = ctypes.CDLL(sys.argv[1])
+lib.krea2_session_validate.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_size_t]
+lib.krea2_last_error.restype = ctypes.c_char_p
+out = []
+for path, tokens, layers in json.loads(sys.argv[2]):
+    status = lib.krea2_session_validate(path.encode(), tokens, layers)
+    out.append([status, lib.krea2_last_error().decode()])
+maps = open("/proc/self/maps").read()
+print(json.dumps({"results": out, "driver_loaded": "libcuda.so" in maps}))
+'''
+
+
+def validate_in_child(calls):
+    """Runs Session::validate in a process that imports neither torch nor anything else that could load the
+    CUDA driver, and reports whether the driver library got mapped (tests/constructor.rs:31-36)."""
+    import json
+    import subprocess
+    import sys
+    from krea2_hrx_b200 import _lib
+    done = subprocess.run([sys.executable, "-c", VALIDATE_CHILD, _lib.LIB_PATH, json.dumps(calls)],
+                          capture_output=True, text=True, check=True)
+    return json.loads(done.stdout.strip().splitlines()[-1])
+
+
+def test_an_incomplete_checkpoint_and_invalid_dimensions_are_refused_before_the_gpu(tmp_path):
+    """tests/constructor.rs:38-66."""
+    path = write(tmp_path, "incomplete.safetensors",
+                 '{"blocks.0.attn.wq.weight":{"dtype":"I8","shape":[16,6144],"data_offsets":[0,98304]}}', bytes(98304))
+    calls = [[str(path), 16, 1]] * 3
+    calls += [[str(path), tokens, layers] for tokens, layers in [(0, 1), (15, 1), (16897, 1), (16, 0), (16, 29), (2 ** 64 - 1, 1)]]
+    calls += [[str(tmp_path), 16, 1]]
+    report = validate_in_child(calls)
+    results = report["results"]
+    for status, message in results[:3]:
+        assert status == 1 and "missing tensor" in message, message
+    for status, message in results[3:9]:
+        assert status == 1, message  # InvalidArgument
+    assert results[9][0] == 1 and ".safetensors" in results[9][1]
+    assert not report["driver_loaded"], "a rejected constructor loaded the CUDA driver"
+
+
+def test_the_interleaved_gate_and_up_rows_are_validated_before_any_allocation(tmp_path):
+    """tests/constructor.rs:68-110: mlp.up carries one scale too few; and separately, weights with no rows."""
+    calls = []
+    for zero_rows in (False, True):
+        entries, offset = [], 0
+        for name in ["attn.wq", "attn.wk", "attn.wv", "attn.gate", "attn.wo", "mlp.gate", "mlp.up", "mlp.down"]:
+            rows = 0 if zero_rows else 16
+            entries.append(f'"blocks.0.{name}.weight":{{"dtype":"I8","shape":[{rows},1],"data_offsets":[{offset},{offset + rows}]}}')
+            offset += rows
+            scales = 15 if name == "mlp.up" else 16
+            entries.append(f'"blocks.0.{name}.weight_scale":{{"dtype":"F32","shape":[{scales}],"data_offsets":[{offset},{offset + scales * 4}]}}')
+            offset += scales * 4
+        path = write(tmp_path, f"tiny{int(zero_rows)}.safetensors", "{" + ",".join(entries) + "}", bytes(offset))
+        calls.append([str(path), 16, 1])
+    report = validate_in_child(calls)
+    (status, message), (zero_status, zero_message) = report["results"]
+    assert status == 1 and "scale count in blocks.0.mlp.up" in message, message
+    assert zero_status == 1 and "invalid weight shape" in zero_message, zero_message
+    assert not report["driver_loaded"], "a rejected constructor loaded the CUDA driver"
