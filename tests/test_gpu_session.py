@@ -193,3 +193,29 @@ def test_full_block_session_equals_the_oracle_chain_around_the_attention_kernel(
     assert so.relative_l2(bits(both), loose) < 6e-2
     assert k.device_status() == 0
     s.close()
+
+
+@pytest.mark.parametrize("tokens", [4608, 16896])
+def test_the_benchmark_sized_chain_matches_the_oracle_on_sampled_tokens(tokens):
+    """Reference dimensions at the benchmark's token count and at the largest the session accepts.  The W8A8
+    chain treats every token on its own (prologues and GEMM rows are per token), so the oracle chain over a
+    sample of rows must equal the same rows of the full forward bit for bit; two forwards must agree in full."""
+    from krea2_hrx_b200 import session
+    dims, layers = session.ModelDims(), 2
+    stream = torch.cuda.current_stream()
+    weights = session.Weights(dims, layers)
+    weights.fill_synthetic(99, stream)
+    s = session.Session(stream, weights, tokens, layers)
+    s.set_attention(False)
+    x, mods, cos, sin = so.make_inputs(dims, tokens, layers, seed=tokens)
+    runs = []
+    for _ in range(2):
+        x_t = torch.from_numpy(x.copy()).view(torch.bfloat16)
+        s.run(stream, x_t, torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+        runs.append(bits(x_t).reshape(tokens, dims.hidden))
+    np.testing.assert_array_equal(runs[0], runs[1])
+    rows = np.unique(np.concatenate([[0, 1, 255, 256, tokens - 257, tokens - 1],
+                                     np.random.default_rng(3).integers(0, tokens, 26)]))
+    want, _ = so.oracle_forward(dims, so.host_weights(weights, layers), x[rows], mods)
+    np.testing.assert_array_equal(runs[0][rows], want)
+    s.close()
