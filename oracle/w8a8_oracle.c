@@ -275,11 +275,37 @@ void oracle_prepare_plain_i8(size_t tokens, const uint16_t *h, int8_t *q, float 
  * Bytes k_size..k_stride of a row are never read. */
 void oracle_gemm_i8_acc(size_t m, const int8_t *a, const int8_t *w, int32_t *acc, size_t k_size,
                         size_t k_stride, size_t n_size) {
+    /* Integer sums are exact in any order, so the loop nest is free: two rows by four columns per pass over
+     * k keep eight independent sums going and reuse every loaded byte four or two times. */
 #pragma omp parallel for schedule(static)
     for (ptrdiff_t nb = 0; nb < (ptrdiff_t)n_size; nb += 16) {
-        for (size_t r = 0; r < m; r++) {
+        const size_t n_end = (size_t)nb + 16 < n_size ? (size_t)nb + 16 : n_size;
+        size_t r = 0;
+        for (; r + 2 <= m; r += 2) {
+            const int8_t *a0 = a + r * k_stride, *a1 = a0 + k_stride;
+            size_t n = (size_t)nb;
+            for (; n + 4 <= n_end; n += 4) {
+                const int8_t *w0 = w + n * k_stride, *w1 = w0 + k_stride, *w2 = w1 + k_stride, *w3 = w2 + k_stride;
+                int32_t s00 = 0, s01 = 0, s02 = 0, s03 = 0, s10 = 0, s11 = 0, s12 = 0, s13 = 0;
+                for (size_t k = 0; k < k_size; k++) {
+                    const int32_t x0 = a0[k], x1 = a1[k], y0 = w0[k], y1 = w1[k], y2 = w2[k], y3 = w3[k];
+                    s00 += x0 * y0, s01 += x0 * y1, s02 += x0 * y2, s03 += x0 * y3;
+                    s10 += x1 * y0, s11 += x1 * y1, s12 += x1 * y2, s13 += x1 * y3;
+                }
+                int32_t *o0 = acc + r * n_size + n, *o1 = o0 + n_size;
+                o0[0] = s00, o0[1] = s01, o0[2] = s02, o0[3] = s03;
+                o1[0] = s10, o1[1] = s11, o1[2] = s12, o1[3] = s13;
+            }
+            for (; n < n_end; n++) {
+                const int8_t *wr = w + n * k_stride;
+                int32_t s0 = 0, s1 = 0;
+                for (size_t k = 0; k < k_size; k++) s0 += (int32_t)a0[k] * wr[k], s1 += (int32_t)a1[k] * wr[k];
+                acc[r * n_size + n] = s0, acc[(r + 1) * n_size + n] = s1;
+            }
+        }
+        for (; r < m; r++) {
             const int8_t *ar = a + r * k_stride;
-            for (size_t n = (size_t)nb; n < (size_t)nb + 16 && n < n_size; n++) {
+            for (size_t n = (size_t)nb; n < n_end; n++) {
                 const int8_t *wr = w + n * k_stride;
                 int32_t s = 0;
                 for (size_t k = 0; k < k_size; k++) s += (int32_t)ar[k] * (int32_t)wr[k];
