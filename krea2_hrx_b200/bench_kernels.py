@@ -187,10 +187,42 @@ def run_sampler(kind, m, dims, iters, warmup, flush):
     return {"kernel": kind, "elements": count, "ms": ms, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6}
 
 
+def run_library(kind, m, dims, iters, warmup, flush):
+    """Calibration, not a product path: the vendor library's int8 GEMM (`torch._int_mm`, raw i32 output, no
+    epilogue) on the q|k|v|gate shape beside this library's fused kernel, each as a short burst and as a
+    3-second back-to-back loop under the power cap."""
+    import time
+    h, n = dims["hidden"], dims["qkv"]
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    a = torch.randint(-127, 128, (m, h), generator=gen, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (n, h), generator=gen, device="cuda", dtype=torch.int8)
+    ws = torch.rand(n, generator=gen, device="cuda") * 1e-2
+    a_s = torch.rand(m, generator=gen, device="cuda") * 1e-2
+    c = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    calls = {"library": lambda: torch._int_mm(a, w.t()), "fused": lambda: ops.gemm_i8_256(m, a, w, ws, a_s, c, h, h, n)}
+    out = {"kernel": "int8 GEMM calibration", "m": m, "n": n, "k": h}
+    bursts = {name: time_launches(fn, iters, warmup, flush) for name, fn in calls.items()}  # before the long loops heat the part
+    for name, fn in calls.items():
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches, began = 0, time.time()
+        start.record()
+        while time.time() - began < 3.0:
+            for _ in range(50):
+                fn()
+            launches += 50
+            torch.cuda.synchronize()
+        end.record()
+        torch.cuda.synchronize()
+        sustained = start.elapsed_time(end) / launches
+        out[name] = {"burst_tops": 2.0 * m * n * h / bursts[name] / 1e9, "sustained_tops": 2.0 * m * n * h / sustained / 1e9}
+    return out
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", default="all",
-                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, euler, guidance, modulation, gemms, prologues or all "
+                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, euler, guidance, modulation, calibration, gemms, prologues or all "
                              "(comma separated)")
     parser.add_argument("--m", default="4608", help="rows, comma separated; 'reference' = the reference's bench list")
     parser.add_argument("--dims", default="reference", choices=sorted(DIMS))
@@ -208,7 +240,8 @@ def main():
         for m in rows:
             runner = run_prologue if kind in ("norm", "gated", "plain") else \
                 run_attention if kind in ("rope", "vt", "attention") else \
-                run_sampler if kind in ("euler", "guidance", "modulation") else run_gemm
+                run_sampler if kind in ("euler", "guidance", "modulation") else \
+                run_library if kind == "calibration" else run_gemm
             result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
             result["dims"] = args.dims
             print(json.dumps(result), flush=True)
