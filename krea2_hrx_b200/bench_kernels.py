@@ -37,7 +37,54 @@ def gemm_case(kind, dims):
             "down": ("gemm_i8_resid_256x256", inter, h), "acc": ("gemm_i8_acc", h, qkv)}[kind]
 
 
+SUSTAIN_SECONDS = 0.0   # --sustain: also run every timed kernel back to back this long, sampling power and clock
+LAST_SUSTAINED = {}
+
+
+def sustained_run(fn, seconds):
+    """Back-to-back launches for `seconds` with nvidia-smi sampling beside them: the mean launch time under the
+    power cap, the median board power and SM clock, and their product, the energy of one launch."""
+    import subprocess
+    import time
+    index = str(torch.cuda.current_device())
+    physical = os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")
+    if physical != [""] and int(index) < len(physical):
+        index = physical[int(index)]
+    sampler = subprocess.Popen(["nvidia-smi", "-i", index, "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits",
+                                "-lms", "100"], stdout=subprocess.PIPE, text=True)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches, began = 0, time.time()
+    start.record()
+    while time.time() - began < seconds:
+        for _ in range(50):
+            fn()
+        launches += 50
+        torch.cuda.synchronize()
+    end.record()
+    torch.cuda.synchronize()
+    sampler.terminate()
+    rows = [line.split(",") for line in sampler.communicate()[0].strip().splitlines() if "," in line]
+    rows = rows[len(rows) // 3:]  # the part is still ramping during the first samples
+    clocks = sorted(float(r[0]) for r in rows)
+    watts = sorted(float(r[1]) for r in rows)
+    ms = start.elapsed_time(end) / launches
+    out = {"sustained_ms": ms}
+    if rows:
+        out.update({"sm_mhz": clocks[len(clocks) // 2], "watts": watts[len(watts) // 2],
+                    "joules_per_launch": watts[len(watts) // 2] * ms * 1e-3})
+    return out
+
+
 def time_launches(fn, iters, warmup, flush):
+    ms = burst_time(fn, iters, warmup, flush)
+    if SUSTAIN_SECONDS > 0:
+        LAST_SUSTAINED.clear()
+        LAST_SUSTAINED.update(sustained_run(fn, SUSTAIN_SECONDS))
+    return ms
+
+
+def burst_time(fn, iters, warmup, flush):
     scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(warmup):
         fn()
@@ -201,7 +248,7 @@ def run_library(kind, m, dims, iters, warmup, flush):
     c = torch.empty((m, n), dtype=torch.float16, device="cuda")
     calls = {"library": lambda: torch._int_mm(a, w.t()), "fused": lambda: ops.gemm_i8_256(m, a, w, ws, a_s, c, h, h, n)}
     out = {"kernel": "int8 GEMM calibration", "m": m, "n": n, "k": h}
-    bursts = {name: time_launches(fn, iters, warmup, flush) for name, fn in calls.items()}  # before the long loops heat the part
+    bursts = {name: burst_time(fn, iters, warmup, flush) for name, fn in calls.items()}  # before the long loops heat the part
     for name, fn in calls.items():
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -229,7 +276,11 @@ def main():
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--flush-l2", action="store_true")
+    parser.add_argument("--sustain", type=float, default=0.0,
+                        help="seconds of back-to-back launches per kernel with power and clock sampling")
     args = parser.parse_args()
+    global SUSTAIN_SECONDS
+    SUSTAIN_SECONDS = args.sustain
     kinds = []
     for item in args.kernel.split(","):
         kinds += {"all": ["qkvg", "wo", "gu", "down", "norm", "gated", "plain"], "gemms": ["qkvg", "wo", "gu", "down"],
@@ -244,6 +295,8 @@ def main():
                 run_library if kind == "calibration" else run_gemm
             result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
             result["dims"] = args.dims
+            if SUSTAIN_SECONDS > 0 and kind != "calibration":
+                result["sustained"] = dict(LAST_SUSTAINED)
             print(json.dumps(result), flush=True)
 
 

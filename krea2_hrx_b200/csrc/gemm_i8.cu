@@ -225,6 +225,7 @@ struct Tile {
 
 struct GemmArgs {
     uint32_t m, n, k_blocks;
+    uint32_t n_group;      // pair kernel: output tile columns walked together (0: all rows of a column first)
     const float *scale;    // [n] per output channel
     const float *a_scale;  // [m] per token
     const float *gate;     // [n], residual epilogue only
@@ -604,6 +605,22 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t m_tiles = (g.m + 2 * kBlockM - 1) / (2 * kBlockM);
     const uint32_t tiles = m_tiles * (g.n / BN);
+    // Tile order.  By default a column of tiles is walked top to bottom before the next one, so the tiles
+    // in flight (74 pairs) share all of A and a few column panels of W: right while A stays in L2.  When A
+    // is larger than that (the down projection: 76 MB), `n_group` column panels are walked row by row
+    // instead, so that this group's W panels stay resident while A streams through once per group.
+    const uint32_t n_tiles = g.n / BN;
+    auto tile_origin = [&](uint32_t tile, uint32_t &tile_m, uint32_t &tile_n) {
+        if (g.n_group == 0) {
+            tile_m = tile % m_tiles;
+            tile_n = tile / m_tiles;
+        } else {
+            const uint32_t per_group = m_tiles * g.n_group, group = tile / per_group, t = tile % per_group;
+            const uint32_t first = group * g.n_group, width = n_tiles - first < g.n_group ? n_tiles - first : g.n_group;
+            tile_m = t / width;
+            tile_n = first + t % width;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < T::kStages; s++) {
@@ -632,8 +649,10 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t stage = 0, phase = 0;
             bool alive = true;
             for (uint32_t tile = pair; alive && tile < tiles; tile += pairs) {
-                const int m0 = static_cast<int>((tile % m_tiles) * 2 * kBlockM + rank * kBlockM);
-                const int n0 = static_cast<int>((tile / m_tiles) * BN + rank * (BN / 2));
+                uint32_t tile_m, tile_n;
+                tile_origin(tile, tile_m, tile_n);
+                const int m0 = static_cast<int>(tile_m * 2 * kBlockM + rank * kBlockM);
+                const int n0 = static_cast<int>(tile_n * BN + rank * (BN / 2));
                 for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
                     if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, kProducerTimedOut)) {
                         alive = false;
@@ -694,7 +713,9 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t local = 0;
         for (uint32_t tile = pair; tile < tiles; tile += pairs, local++) {
             const uint32_t a = local & 1u, a_phase = (local >> 1) & 1u;
-            const uint32_t m0 = (tile % m_tiles) * 2 * kBlockM + rank * kBlockM, n0 = (tile / m_tiles) * BN;
+            uint32_t tile_m, tile_n;
+            tile_origin(tile, tile_m, tile_n);
+            const uint32_t m0 = tile_m * 2 * kBlockM + rank * kBlockM, n0 = tile_n * BN;
             const bool ready = mbar_wait(acc_full + a, a_phase, abort_flag, kEpilogueTimedOut);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
@@ -900,6 +921,23 @@ int check_shard(const char *name, const krea2_shard *shard, size_t out_columns) 
     return KREA2_OK;
 }
 
+// How many 256-column tile panels of W the two-CTA kernel walks together (0 = one column of tiles at a
+// time).  With the default order the tiles in flight share all of A; once A is larger than what stays in
+// L2 beside the streaming W (measured: the down projection, 76 MB of A, read 626 MB from DRAM instead of
+// 233 MB) the panels of a group are kept resident instead and A streams through once per group.
+uint32_t tile_column_group(size_t m, size_t k_size, size_t n_size) {
+    static const long forced = [] {
+        const char *text = std::getenv("KREA2_GEMM_NGROUP");
+        return text ? std::strtol(text, nullptr, 10) : -1L;
+    }();
+    if (forced >= 0) return static_cast<uint32_t>(forced);
+    const size_t a_bytes = m * k_size, panel_bytes = 256 * k_size;
+    if (a_bytes <= (size_t(48) << 20)) return 0;
+    const size_t group = (size_t(48) << 20) / panel_bytes;
+    const size_t panels = n_size / 256;
+    return static_cast<uint32_t>(group < 1 ? 1 : (group >= panels ? 0 : group));
+}
+
 template <Epi E>
 int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, const void *w, const float *scale,
              const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride, size_t n_size,
@@ -916,6 +954,7 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n_size);
     args.k_blocks = static_cast<uint32_t>((k_size + kBlockK - 1) / kBlockK);
+    args.n_group = tile_column_group(m, k_size, n_size);
     args.scale = scale;
     args.a_scale = a_scale;
     args.gate = gate;
