@@ -75,7 +75,11 @@ class Checkpoint:
             lib().krea2_checkpoint_close(self._handle)
             self._handle = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except TypeError:  # interpreter shutdown: the module globals are already gone
+            pass
 
 
 class Plan:

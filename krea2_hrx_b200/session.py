@@ -93,9 +93,12 @@ class Weights:
                                          host.numel() * host.element_size(), _stream_ptr(stream)))
 
     def __del__(self):
-        if getattr(self, "_handle", None):
-            lib().krea2_weights_release(self._handle)
-            self._handle = None
+        try:
+            if getattr(self, "_handle", None):
+                lib().krea2_weights_release(self._handle)
+                self._handle = None
+        except TypeError:  # interpreter shutdown: the module globals are already gone
+            pass
 
 
 def validate(checkpoint_path, tokens: int, layers: int) -> None:
@@ -180,4 +183,7 @@ class Session:
             self._handle = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except TypeError:  # interpreter shutdown: the module globals are already gone
+            pass
