@@ -125,10 +125,12 @@ def test_production_attention_tiles_match_grouped_cpu_softmax(ops, tokens):
     np.testing.assert_array_equal(again, out)
 
 
-@pytest.mark.parametrize("tokens,qh,kvh", [(300, 8, 2), (1043, 8, 2), (129, 4, 4)])
+@pytest.mark.parametrize("tokens,qh,kvh", [(300, 8, 2), (1043, 8, 2), (129, 4, 4), (127, 4, 2), (128, 4, 2), (255, 4, 2),
+                                           (256, 4, 2), (257, 4, 2), (384, 2, 1), (385, 2, 1), (511, 2, 2), (640, 2, 1)])
 def test_attention_on_seeded_heads(ops, tokens, qh, kvh):
     """Several key tiles, a ragged last tile, grouped heads; scores spread enough that the running
-    maximum moves between tiles."""
+    maximum moves between tiles.  Token counts on both sides of the 128-key tile and of the 256 query rows a
+    block owns: a second query tile that is empty, one row long, full."""
     from krea2_hrx_b200 import shape
     rng = np.random.default_rng(tokens)
     capacity = shape.capacity(tokens)
