@@ -185,3 +185,13 @@ def test_cpp_host_mirror_compiles_and_agrees(tmp_path):
                     f"-Wl,-rpath,{lib_dir}"], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0 and "host mirror ok" in out.stdout, out.stdout + out.stderr
+
+
+def test_the_public_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own, with no C++ or torch types."""
+    import subprocess
+    source = tmp_path / "header_check.c"
+    source.write_text('#include "krea2_b200.h"\nint main(void) { krea2_span_info span; krea2_dims dims; (void)span; (void)dims; '
+                      "return krea2_shape_gemm_pitch(8192) == 8256 ? 0 : 1; }\n")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-fsyntax-only", "-I",
+                    os.path.join(ROOT, "include"), str(source)], check=True)
