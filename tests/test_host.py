@@ -195,3 +195,18 @@ def test_the_public_header_is_plain_c(tmp_path):
                       "return krea2_shape_gemm_pitch(8192) == 8256 ? 0 : 1; }\n")
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-fsyntax-only", "-I",
                     os.path.join(ROOT, "include"), str(source)], check=True)
+
+
+def test_the_reference_arm_prints_the_benchmark_line(tmp_path):
+    """`bench.py --impl reference` (the CPU port on the host cores) keeps the JSON contract of the GPU arm."""
+    import json
+    import subprocess
+    import sys
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                           "--cpu-tokens", "64"], capture_output=True, text=True, check=True, cwd=str(tmp_path))
+    line = json.loads(done.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "w8a8_path_int8_tops" and line["unit"] == "TOP/s"
+    assert line["value"] > 0 and line["higher_is_better"] is True and line["vs_baseline"] is None
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"]
