@@ -9,15 +9,14 @@
 //                                    which computes the same function on 32-row groups)
 //
 // Attention is a flash-attention forward on the fifth-generation tensor cores: one CTA per
-// (128 query rows, query head); S = Q K^T and O += P V are tcgen05.mma kind::f16 with f32
-// accumulators in tensor memory, K and V^T tiles of 128 keys arrive by TMA (128-byte swizzle,
-// two stages each), softmax warps read S from tensor memory (one query row per thread),
-// keep the running maximum and sum in registers and hand P to the second product through shared
-// memory.  O stays in tensor memory across key tiles; it is rescaled there only when a row's
+// (256 query rows, query head), two softmax groups of four warps owning 128 rows each; S = Q K^T
+// and O += P V are tcgen05.mma kind::f16 with f32 accumulators in tensor memory, K and V^T tiles of
+// 128 keys arrive by TMA (128-byte swizzle, two stages each) and serve both groups, softmax warps
+// read S from tensor memory (one query row per thread), keep the running maximum and sum in
+// registers and write P back into tensor memory, where the second product reads it as its A
+// operand.  O stays in tensor memory across key tiles; it is rescaled there only when a row's
 // maximum moves by more than 2^8 (the reference maximum used for the exponentials is otherwise
-// left stale, which changes neither O nor the sum's ratio).  Two softmax groups of four warps take
-// alternate key tiles, each with its own S buffer, P tile, O accumulator, maximum and sum, so that
-// one group's exponentials run while the other waits for scores; the halves are merged at the end.
+// left stale, which changes neither O nor the sum's ratio).  The details are at the kernel.
 #include <cuda.h>
 
 #include <mutex>
