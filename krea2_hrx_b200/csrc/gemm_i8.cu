@@ -11,7 +11,9 @@
 //               i32 -> f32, weight-channel and token scales, the bf16 rounding points of
 //               the reference and the residual / SwiGLU / plain store
 // Two accumulators alternate in tensor memory, so the epilogue of one tile runs under the
-// main loop of the next.  No cluster is launched and no load is multicast.
+// main loop of the next.  The default variant for N a multiple of 256 pairs two CTAs in a cluster
+// on one 256 x 256 tile (tcgen05.mma.cta_group::2, each CTA loading its own halves of A and W);
+// no load is multicast.
 //
 // Every wait on an mbarrier is bounded in time; a wait that runs out raises a CTA-wide
 // abort flag and a device status word, the roles fall through to the common teardown, the
