@@ -29,6 +29,7 @@ constexpr unsigned kFull = 0xffffffffu;
 constexpr int kSmemLimit = 232448;       // opt-in dynamic shared memory of one sm_100 block
 constexpr int kWideThreads = 1024;       // block size limit of the f32 prologues
 constexpr int kPlainThreads = 1024;      // of the f16 prologue
+constexpr int kSlotFloats = 40;          // per worker and parity: 32 per-warp maxima, the reciprocal, padding
 
 template <int CPL, int MAX_THREADS>
 struct Geometry {
@@ -262,6 +263,29 @@ __device__ __forceinline__ void store_codes(const F2 (&v)[8], float inv, int8_t 
     *reinterpret_cast<uint2 *>(second) = make_uint2(pack_s8x4(cb[0], cb[1], cb[2], cb[3]), pack_s8x4(cb[4], cb[5], cb[6], cb[7]));
 }
 
+// From the threads' absmax to the row's scale and its reciprocal.  The warps' maxima meet in `slots`
+// (32 floats, then two for the results); the worker's first warp alone reduces them and does the two
+// divisions, the others wait at a second barrier and read the reciprocal, so the scalar work is issued once
+// per row instead of once per warp.  `slots` is double-buffered by the caller.
+template <int WARPS>
+__device__ __forceinline__ float row_reciprocal(float amax, float rotation, float *slots, int worker, int warp_in_worker,
+                                                int lane, float *scale_out) {
+    amax = warp_max(amax);
+    if (lane == 0) slots[warp_in_worker] = amax;
+    worker_barrier(worker, 32 * WARPS);
+    if (warp_in_worker == 0) {
+        const float m = warp_max(lane < WARPS ? slots[lane] : 0.0f);
+        float s, inv;
+        row_scale(m, rotation, s, inv);
+        if (lane == 0) {
+            slots[32] = inv;
+            *scale_out = s;
+        }
+    }
+    worker_barrier(worker, 32 * WARPS);
+    return slots[32];
+}
+
 // Row absmax over the worker (per-warp maxima in `slots`, double-buffered by the caller),
 // then the codes of the thread's 32 positions and the row scale.
 template <int WARPS>
@@ -272,18 +296,10 @@ __device__ __forceinline__ void quantise_f32(F2 (&x)[2][8], float *slots, int wo
     for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
         for (int e = 0; e < 8; e++) amax = fmaxf(amax, fmaxf(fabsf(x[c1][e].a), fabsf(x[c1][e].b)));
-    amax = warp_max(amax);
-    if (lane == 0) slots[warp_in_worker] = amax;
-    worker_barrier(worker, 32 * WARPS);
-    float m = slots[0];
-#pragma unroll
-    for (int i = 1; i < WARPS; i++) m = fmaxf(m, slots[i]);
-    float s, inv;
-    row_scale(m, 0.0625f, s, inv);
+    const float inv = row_reciprocal<WARPS>(amax, 0.0625f, slots, worker, warp_in_worker, lane, scale_out);
 #pragma unroll
     for (int c1 = 0; c1 < 2; c1++)
         store_codes(x[c1], inv, q_row + 8 * layout.chunk(0, c1), q_row + 8 * layout.chunk(1, c1));
-    if (warp_in_worker == 0 && lane == 0) *scale_out = s;
 }
 
 // The rows of one block and of one worker in it: blocks split the rows evenly, workers
@@ -301,7 +317,7 @@ template <int CPL>
 struct NormPlan {
     using G = Geometry<CPL, kWideThreads>;
     static constexpr int kRowBytes = 2 * G::kWorkers * G::kWidth * 2;  // two buffers per worker
-    static constexpr int kSmallBytes = G::kWorkers * (8 + 2 * 32) * 4;
+    static constexpr int kSmallBytes = G::kWorkers * (12 + 2 * kSlotFloats) * 4;
     static constexpr int kVectorBytes = G::kWidth * (4 + 4 + 2);
     static constexpr bool kStaged = kVectorBytes + kRowBytes + kSmallBytes <= kSmemLimit;
     static constexpr int kBytes = (kStaged ? kVectorBytes : 0) + kRowBytes + kSmallBytes;
@@ -341,7 +357,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     uint4 *vec_mod = reinterpret_cast<uint4 *>(vec_shift + width);  // one 16-byte unit per chunk
     uint4 *row_store = reinterpret_cast<uint4 *>(smem + (Plan::kStaged ? Plan::kVectorBytes : 0));
     float *sum_store = reinterpret_cast<float *>(row_store + 2 * G::kWorkers * G::kChunks);
-    float *max_store = sum_store + G::kWorkers * 8;
+    float *max_store = sum_store + G::kWorkers * 12;
 
     if constexpr (Plan::kStaged) {
         for (int chunk = threadIdx.x; chunk < G::kChunks; chunk += G::kBlockThreads) {
@@ -368,8 +384,8 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
     uint4 *row_bufs = row_store + 2 * worker * G::kChunks;
-    float *sums = sum_store + worker * 8;
-    float *maxes = max_store + worker * 64;
+    float *sums = sum_store + worker * 12;  // eight wave sums, then the row's 1 / rms
+    float *maxes = max_store + worker * 2 * kSlotFloats;
     int parity = 0;
 
     // The next row streams into the worker's other buffer (16-byte asynchronous copies, slot-swizzled)
@@ -388,7 +404,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
     }
     worker_barrier(worker, G::kWorkerThreads);
 
-    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= kSlotFloats) {
         const size_t row = rows.next;
         const uint4 *row_buf = row_bufs + (parity ? G::kChunks : 0);
         if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, parity ? 0 : 1);
@@ -416,11 +432,16 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
             }
         }
         worker_barrier(worker, G::kWorkerThreads);
-        // The eight waves in the reference's written order (:126-138).
-        float total = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[4]), __fadd_rn(sums[2], sums[6])),
-                                __fadd_rn(__fadd_rn(sums[1], sums[5]), __fadd_rn(sums[3], sums[7])));
-        float mean_eps = __fadd_rn(__fdiv_rn(total, static_cast<float>(width)), eps);
-        float rinv = __fdiv_rn(1.0f, __fsqrt_rn(mean_eps));
+        if (warp == 0) {
+            // The eight waves in the reference's written order (:126-138); one warp does the divisions and
+            // the square root for the row.
+            float total = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[4]), __fadd_rn(sums[2], sums[6])),
+                                    __fadd_rn(__fadd_rn(sums[1], sums[5]), __fadd_rn(sums[3], sums[7])));
+            float mean_eps = __fadd_rn(__fdiv_rn(total, static_cast<float>(width)), eps);
+            if (lane == 0) sums[8] = __fdiv_rn(1.0f, __fsqrt_rn(mean_eps));
+        }
+        worker_barrier(worker, G::kWorkerThreads);
+        const float rinv = sums[8];
 
         F2 x[2][8];
 #pragma unroll
@@ -502,7 +523,7 @@ constexpr int kTableBytes = 65536 * 2;
 template <int CPL>
 struct GatedPlan {
     using G = Geometry<CPL, kWideThreads>;
-    static constexpr int kBytes = kTableBytes + G::kWorkers * 2 * 32 * 4 + 16;
+    static constexpr int kBytes = kTableBytes + G::kWorkers * 2 * kSlotFloats * 4 + 16;
 };
 
 template <int CPL>
@@ -515,7 +536,7 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
     extern __shared__ __align__(16) uint8_t smem[];
     uint16_t *table = reinterpret_cast<uint16_t *>(smem);
     float *max_store = reinterpret_cast<float *>(smem + kTableBytes);
-    int *ready = reinterpret_cast<int *>(max_store + G::kWorkers * 64);
+    int *ready = reinterpret_cast<int *>(max_store + G::kWorkers * 2 * kSlotFloats);
 
     if (threadIdx.x == 0) {
         int flag;
@@ -535,10 +556,10 @@ prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restri
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
-    float *maxes = max_store + worker * 64;
+    float *maxes = max_store + worker * 2 * kSlotFloats;
     int parity = 0;
 
-    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
+    for (Rows rows = worker_rows(tokens, worker); rows.next < rows.end; rows.next += G::kWorkers, parity ^= kSlotFloats) {
         const size_t row = rows.next;
         const uint4 *a_src = reinterpret_cast<const uint4 *>(attn + row * attn_stride);
         const uint4 *g_src = reinterpret_cast<const uint4 *>(gate + row * gate_stride);
@@ -602,7 +623,7 @@ template <int CPL>
 struct PlainPlan {
     using G = Geometry<CPL, kPlainThreads>;
     static constexpr int kStageBytes = 2 * 4 * 16 * G::kBlockThreads;  // two rows of four chunks per thread
-    static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * 32 * 4;
+    static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * kSlotFloats * 4;
 };
 
 template <int CPL>
@@ -618,7 +639,7 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
     const int worker = threadIdx.x / G::kWorkerThreads, t = threadIdx.x % G::kWorkerThreads;
     const int lane = t & 31, warp = t >> 5;
     const Layout layout = make_layout(warp, lane);
-    float *maxes = max_store + worker * 64;
+    float *maxes = max_store + worker * 2 * kSlotFloats;
     int parity = 0;
 
     // Each thread streams its own four chunks of the next row into shared memory while it works
@@ -634,7 +655,7 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
     Rows rows = worker_rows(tokens, worker);
     if (rows.next < rows.end) fetch(rows.next, 0);
 
-    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= 32) {
+    for (; rows.next < rows.end; rows.next += G::kWorkers, parity ^= kSlotFloats) {
         const size_t row = rows.next;
         const int buffer = parity ? 1 : 0;
         copy_async_wait();
@@ -673,14 +694,8 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
 #pragma unroll
             for (int e = 0; e < 8; e++)
                 packed_max = __hmax2(packed_max, __habs2(*reinterpret_cast<const __half2 *>(&x[c1][e])));
-        float amax = warp_max(fmaxf(__low2float(packed_max), __high2float(packed_max)));
-        if (lane == 0) maxes[parity + warp] = amax;
-        worker_barrier(worker, G::kWorkerThreads);
-        float m = maxes[parity];
-#pragma unroll
-        for (int i = 1; i < kWarps; i++) m = fmaxf(m, maxes[parity + i]);
-        float s, inv;
-        row_scale(m, 16.0f, s, inv);
+        const float inv = row_reciprocal<kWarps>(fmaxf(__low2float(packed_max), __high2float(packed_max)), 16.0f, maxes + parity,
+                                                 worker, warp, lane, q_scale + row);
         int8_t *q_row = q + row * out_stride;
 #pragma unroll
         for (int c1 = 0; c1 < 2; c1++) {
@@ -689,7 +704,6 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
             for (int e = 0; e < 8; e++) v[e] = unpack_f16x2(x[c1][e]);
             store_codes(v, inv, q_row + 8 * layout.chunk(0, c1), q_row + 8 * layout.chunk(1, c1));
         }
-        if (warp == 0 && lane == 0) q_scale[row] = s;
     }
 }
 
