@@ -92,3 +92,35 @@ def test_sharded_chain_on_two_gpus_fused_and_nccl():
                             capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
     assert "tp check ok" in result.stdout
+
+
+def test_a_wait_for_a_peer_that_never_publishes_gives_up_and_reports_it():
+    """Failure detection without a fault: slot 1 of the flag array is never written (a peer that died between
+    steps), so the bounded wait runs out after its two seconds, raises the device status word and returns; the
+    context stays usable and the next read of the status is clean."""
+    import time
+    from krea2_hrx_b200._lib import check, lib
+    assert k.device_status() == 0
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags[0] = 1  # this rank's own slab has "landed"
+    stream = torch.cuda.current_stream()
+    began = time.time()
+    check(lib().krea2_shard_wait(stream.cuda_stream, flags.data_ptr(), 2, 1, None))
+    status = k.device_status()  # synchronises
+    waited = time.time() - began
+    assert status & 16, f"status word {status}: the wait did not report that it gave up"
+    assert 1.5 < waited < 10.0, f"the wait took {waited:.1f} s against a limit of 2 s"
+    assert k.device_status() == 0, "the status word is cleared by reading it"
+    # the device still computes
+    from krea2_hrx_b200 import ops
+    a = torch.randint(-127, 128, (64, 128), device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (128, 128), device="cuda", dtype=torch.int8)
+    acc = torch.zeros((64, 128), dtype=torch.int32, device="cuda")
+    ops.gemm_i8_acc(64, a, w, acc, 128, 128, 128)
+    torch.cuda.synchronize()
+    want = a.cpu().to(torch.int64) @ w.cpu().to(torch.int64).t()
+    assert torch.equal(acc.cpu().to(torch.int64), want)
+    # once the peer's slot is set the same wait returns at once
+    flags[1] = 1
+    check(lib().krea2_shard_wait(stream.cuda_stream, flags.data_ptr(), 2, 1, None))
+    assert k.device_status() == 0
