@@ -163,3 +163,34 @@ def test_attention_at_the_session_shape_on_sampled_rows(ops):
     rows = [0, 127, 128, 2303, 4480, 4607]
     want = oracle.attention_gqa(bits(q[rows]), bits(kk), bits(v), qh, kvh, scale)
     kat.close(kat.f16_from_bits(bits(out[rows])).astype(np.float64), want, 2e-2, 2e-2)
+
+
+def test_attention_repeated_dispatch_is_deterministic(ops):
+    """The reference's race check (tests/softmax_repeat.rs) for the attention kernel: the same launch, repeated
+    while other work keeps the device busy, gives the same bytes every time.  The kernel orders its products
+    and softmax passes through the tensor pipe's issue order; a slip there would show up as run-to-run noise."""
+    from krea2_hrx_b200 import shape
+    tokens, qh, kvh = 2311, 24, 6
+    capacity = shape.capacity(tokens)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    q = (torch.randn((tokens, qh * 128), generator=gen, device="cuda") * 1.5).to(torch.float16)
+    kk = (torch.randn((tokens, kvh * 128), generator=gen, device="cuda") * 1.5).to(torch.float16)
+    v = torch.randn((tokens, kvh * 128), generator=gen, device="cuda").to(torch.float16)
+    vt = torch.zeros((kvh * 128, capacity), dtype=torch.float16, device="cuda")
+    ops.v_transpose(v, vt, kvh * 128, capacity)
+    scale = 1.0 / np.sqrt(128)
+    first = None
+    busy = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    for i in range(8):
+        out = torch.zeros((tokens, qh * 128), dtype=torch.float16, device="cuda")
+        if i % 2:
+            busy.fill_(i)  # a different cache and memory state in front of every other launch
+        ops.attention_gqa(tokens, kvh, q, kk, vt, out, qh * 128, kvh * 128, qh * 128, capacity, scale)
+        got = bits(out)
+        if first is None:
+            first = got
+            rows = [0, 255, 256, 1155, 2310]
+            want = oracle.attention_gqa(bits(q[rows]), bits(kk), bits(v), qh, kvh, scale)
+            kat.close(kat.f16_from_bits(got[rows]).astype(np.float64), want, 2e-2, 2e-2)
+        else:
+            np.testing.assert_array_equal(got, first)
