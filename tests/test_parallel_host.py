@@ -63,3 +63,22 @@ def test_two_gloo_ranks_reassemble_column_slabs():
         p.join(120)
         assert p.exitcode == 0
     assert failures.empty(), failures.get()
+
+
+def test_the_reference_arm_under_two_ranks_prints_one_line():
+    """`bench.py --impl reference --gpus 2` under torchrun: rank 0 alone times the CPU port and prints the line,
+    the other rank exits 0 without work."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(root, "bench.py"),
+                           "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0", "--cpu-tokens", "32"],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 1 and lines[0]["impl"] == "reference" and lines[0]["n_gpus"] == 2
