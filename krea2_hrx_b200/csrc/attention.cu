@@ -258,6 +258,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 // K-major operand tile of 128-byte swizzled rows, eight rows per 1024-byte atom (as in the GEMM).
 __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
@@ -449,13 +454,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int i = 0; i < kTile; i++)
                     if (static_cast<uint32_t>(i) >= valid) v[i] = -INFINITY;
             }
+            // Eight running maxima, two new scores each per 3-input max.
             float part[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) part[i] = v[i];
+            for (int i = 0; i < 8; i++) part[i] = max3(v[i], v[i + 8], v[i + 16]);
 #pragma unroll
-            for (int i = 8; i < kTile; i++) part[i & 7] = fmaxf(part[i & 7], v[i]);
-            float tile_max = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
-                                   fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+            for (int i = 24; i < kTile - 8; i += 16)
+#pragma unroll
+                for (int k = 0; k < 8; k++) part[k] = max3(part[k], v[i + k], v[i + 8 + k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) part[k] = fmaxf(part[k], v[kTile - 8 + k]);
+            float tile_max = fmaxf(max3(part[0], part[1], part[2]), max3(max3(part[3], part[4], part[5]), part[6], part[7]));
             tile_max *= g.scale_log2;
             // The exponent reference moves only when the maximum has grown by more than 2^8.
             float alpha = 1.0f;
