@@ -91,6 +91,19 @@ struct Parser {
     void space() {
         while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++;
     }
+    // Four hex digits after the 'u' that p points at; leaves p on the last digit.
+    bool hex4(unsigned &code) {
+        if (end - p < 5) return fail_at("short \\u escape in the header");
+        code = 0;
+        for (int i = 1; i <= 4; i++) {
+            const char c = p[i];
+            code = code * 16 + (c >= '0' && c <= '9' ? c - '0' : c >= 'a' && c <= 'f' ? c - 'a' + 10
+                                : c >= 'A' && c <= 'F' ? c - 'A' + 10 : 0x10000);
+        }
+        if (code > 0xffff) return fail_at("bad \\u escape in the header");
+        p += 4;
+        return true;
+    }
     bool string(std::string &out) {
         if (p >= end || *p != '"') return fail_at("a string was expected in the header");
         p++;
@@ -107,21 +120,28 @@ struct Parser {
                     case 'r': out += '\r'; break;
                     case 't': out += '\t'; break;
                     case 'u': {
-                        if (end - p < 5) return fail_at("short \\u escape in the header");
                         unsigned code = 0;
-                        for (int i = 1; i <= 4; i++) {
-                            const char c = p[i];
-                            code = code * 16 + (c >= '0' && c <= '9' ? c - '0' : c >= 'a' && c <= 'f' ? c - 'a' + 10
-                                                : c >= 'A' && c <= 'F' ? c - 'A' + 10 : 256);
+                        if (!hex4(code)) return false;
+                        if (code >= 0xdc00 && code <= 0xdfff) return fail_at("lone surrogate in the header");
+                        if (code >= 0xd800 && code <= 0xdbff) {  // a pair encodes one character above U+FFFF
+                            unsigned low = 0;
+                            if (end - p < 3 || p[1] != '\\' || p[2] != 'u') return fail_at("lone surrogate in the header");
+                            p += 2;
+                            if (!hex4(low)) return false;
+                            if (low < 0xdc00 || low > 0xdfff) return fail_at("lone surrogate in the header");
+                            code = 0x10000 + ((code - 0xd800) << 10) + (low - 0xdc00);
                         }
-                        if (code > 0xffff) return fail_at("bad \\u escape in the header");
-                        p += 4;
                         if (code < 0x80) out += static_cast<char>(code);
                         else if (code < 0x800) {
                             out += static_cast<char>(0xc0 | (code >> 6));
                             out += static_cast<char>(0x80 | (code & 0x3f));
-                        } else {
+                        } else if (code < 0x10000) {
                             out += static_cast<char>(0xe0 | (code >> 12));
+                            out += static_cast<char>(0x80 | ((code >> 6) & 0x3f));
+                            out += static_cast<char>(0x80 | (code & 0x3f));
+                        } else {
+                            out += static_cast<char>(0xf0 | (code >> 18));
+                            out += static_cast<char>(0x80 | ((code >> 12) & 0x3f));
                             out += static_cast<char>(0x80 | ((code >> 6) & 0x3f));
                             out += static_cast<char>(0x80 | (code & 0x3f));
                         }
@@ -131,6 +151,7 @@ struct Parser {
                 }
                 p++;
             } else {
+                if (static_cast<unsigned char>(*p) < 0x20) return fail_at("control character in a header string");
                 out += *p++;
             }
         }
@@ -208,6 +229,28 @@ struct Parser {
     }
 };
 
+// Whether the bytes are well-formed UTF-8 (no overlong forms, no surrogates, nothing above U+10FFFF):
+// JSON text is UTF-8, and tensor names leave this library as C strings.
+bool valid_utf8(const uint8_t *p, const uint8_t *end) {
+    while (p < end) {
+        const uint8_t lead = *p++;
+        if (lead < 0x80) continue;
+        int tail;
+        uint32_t code, least;
+        if ((lead & 0xe0) == 0xc0) tail = 1, code = lead & 0x1f, least = 0x80;
+        else if ((lead & 0xf0) == 0xe0) tail = 2, code = lead & 0x0f, least = 0x800;
+        else if ((lead & 0xf8) == 0xf0) tail = 3, code = lead & 0x07, least = 0x10000;
+        else return false;
+        if (end - p < tail) return false;
+        for (int i = 0; i < tail; i++) {
+            if ((*p & 0xc0) != 0x80) return false;
+            code = (code << 6) | (*p++ & 0x3f);
+        }
+        if (code < least || code > 0x10ffff || (code >= 0xd800 && code <= 0xdfff)) return false;
+    }
+    return true;
+}
+
 size_t dtype_bytes(const std::string &dtype) {
     static const std::pair<const char *, size_t> kTable[] = {
         {"BOOL", 1}, {"U8", 1}, {"I8", 1}, {"F8_E5M2", 1}, {"F8_E4M3", 1}, {"I16", 2}, {"U16", 2}, {"F16", 2},
@@ -250,6 +293,7 @@ int read_header(krea2_checkpoint &c) {
     if (header_bytes > c.file_bytes - 8) return unreadable(c.path, "the header is longer than the file");
     c.data_start = 8 + static_cast<size_t>(header_bytes);
     const size_t data_bytes = c.file_bytes - c.data_start;
+    if (!valid_utf8(c.map + 8, c.map + c.data_start)) return unreadable(c.path, "the header is not UTF-8");
     Parser parser{reinterpret_cast<const char *>(c.map + 8), reinterpret_cast<const char *>(c.map + c.data_start), {}};
     Json root;
     if (!parser.value(root, 0)) return unreadable(c.path, parser.error);

@@ -76,6 +76,21 @@ def test_malformed_headers_are_refused(tmp_path):
             Checkpoint(write(tmp_path, f"bad{i}.safetensors", header, bytes(8)))
 
 
+def test_header_strings_must_be_well_formed_text(tmp_path):
+    """JSON text is UTF-8 without raw control characters, and an escaped surrogate needs its pair."""
+    entry = b'{"dtype":"I8","shape":[1],"data_offsets":[0,1]}'
+    for i, name in enumerate([b'w\x9a', b'w\xc0\xaf', b'w\xed\xa0\x80', b'w\x01', b'w\\ud83d', b'w\\ude00', b'w\\ud83dx']):
+        path = tmp_path / f"text{i}.safetensors"
+        header = b'{"' + name + b'":' + entry + b'}'
+        path.write_bytes(len(header).to_bytes(8, "little") + header + bytes(8))
+        with pytest.raises(k.InvalidArgument, match=r"^cannot read "):
+            Checkpoint(path)
+    header = b'{"w\\ud83d\\ude00\\u00e9\xc3\xa9":' + entry + b'}'
+    path = tmp_path / "pair.safetensors"
+    path.write_bytes(len(header).to_bytes(8, "little") + header + bytes(8))
+    assert Checkpoint(path).names() == ["w\U0001f600\u00e9\u00e9"]
+
+
 SMALL = dict(layers=2, hidden=2048, kv_heads=2, head_dim=128, inter=8192)
 
 
