@@ -368,9 +368,9 @@ int krea2_session_run_device(krea2_session *session, krea2_stream stream, void *
 int krea2_session_buffer(const krea2_session *session, const char *name, void **ptr, size_t *bytes);
 
 /* Chooses between the full block (1, the default where the head shape allows: 128 channels per
- * head) and the W8A8 chain alone (0): QK-norm + RoPE, V transpose and attention replaced by a
- * copy of the query columns into the attention output, which keeps every remaining stage
- * reproducible bit for bit on a CPU.  Returns the previous setting; a recorded graph is dropped. */
+ * head) and the W8A8 chain alone (0): QK-norm + RoPE, V transpose and attention are left out and
+ * the gated prologue reads the query columns of the q|k|v|gate output in place of an attention
+ * output, which keeps every remaining stage reproducible bit for bit on a CPU.  Returns the previous setting; a recorded graph is dropped. */
 int krea2_session_set_attention(krea2_session *session, int enable);
 
 /* Number of kernels of this library that one forward of `layers` blocks launches. */

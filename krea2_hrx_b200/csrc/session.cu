@@ -7,8 +7,8 @@
 // GEMM, QK-norm + RoPE, V transpose, fp16 attention, prepare_gated, wo GEMM + residual,
 // prepare_norm, gate|up GEMM + SwiGLU, prepare_plain, down GEMM + residual.  With attention
 // switched off (krea2_session_set_attention) the three launches that are not W8A8 products are
-// replaced by a copy of the query columns of the fused buffer into the attention output: the
-// W8A8 chain alone, which the CPU oracle reproduces bit for bit.
+// left out and the gated prologue reads the query columns of the fused buffer in place of an
+// attention output: the W8A8 chain alone, which the CPU oracle reproduces bit for bit.
 #include <atomic>
 #include <cstdlib>
 #include <map>
@@ -150,7 +150,7 @@ struct krea2_session {
     size_t q_bytes = 0, kv_bytes = 0;
     cudaGraphExec_t graph = nullptr;
     bool profile = false, poisoned = false;
-    bool attention = true;  // false: the W8A8 chain alone, a copy of the query columns in attention's place
+    bool attention = true;  // false: the W8A8 chain alone, the query columns in the attention output's place
     bool rope_valid = false;
     uint64_t rope_print[2] = {0, 0};
     std::vector<Stage> stages;

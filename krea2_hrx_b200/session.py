@@ -137,7 +137,7 @@ class Session:
         return bool(lib().krea2_session_set_profile(self._handle, int(enable)))
 
     def set_attention(self, enable: bool) -> bool:
-        """Full block (True) or the W8A8 chain with a copy in attention's place (False)."""
+        """Full block (True) or the W8A8 chain alone, the query columns in the attention output's place (False)."""
         return bool(lib().krea2_session_set_attention(self._handle, int(enable)))
 
     def stage_profile(self) -> List[Tuple[str, float]]:

@@ -31,8 +31,8 @@ def oracle_forward(dims, blocks, x_bits, mods, first=0, count=None, attention=Fa
     and the intermediates of the last block.  With `attention` the three launches between the
     q|k|v|gate GEMM and the gated prologue are the oracle's RoPE (exact) and float64 attention
     (a tolerance reference) or, when `attention` is a function, whatever it returns for (q, k, v,
-    q_heads, kv_heads); without, the copy of the query columns the session uses when its
-    attention is switched off, which keeps the whole chain bit-exact."""
+    q_heads, kv_heads); without, the query columns take the attention output's place, as in a
+    session whose attention is switched off, which keeps the whole chain bit-exact."""
     from krea2_hrx_b200 import shape
     hidden, inter = dims.hidden, dims.inter
     qkvg, gate_offset = dims.qkvg, dims.gate_offset
