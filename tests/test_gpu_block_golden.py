@@ -1,0 +1,55 @@
+"""The CUDA session, attention on, against the reference's own torch block (tests/golden/block_w8a8.npz,
+made by tests/golden/make_block_golden.py from `Krea2Ref.block`, scripts/quantized_reference.py:262-268).
+
+The seeded weights of tests/block_case.py are written as a checkpoint file under the checkpoint's own
+tensor names, loaded through the library's checkpoint path at the reference's dimensions, and one and
+two blocks are run from host buffers.  Relative RMS is the reference's measure between its kernels and
+this torch code: 0.0117 over 28 blocks (docs/testing.md:226)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import block_case
+import session_oracle
+from oracle import plan as plan_oracle
+
+pytestmark = pytest.mark.gpu
+
+k = pytest.importorskip("krea2_hrx_b200")
+from krea2_hrx_b200 import session  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "block_w8a8.npz")
+BOUNDS = {1: 0.008, 2: 0.0117}
+
+
+@pytest.fixture(scope="module")
+def loaded(tmp_path_factory):
+    tensors = block_case.block_tensors()
+    path = tmp_path_factory.mktemp("block") / "krea2_block_case.safetensors"
+    plan_oracle.write_safetensors(str(path), tensors, metadata={"format": "pt"})
+    weights = session.Weights.load(path, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    os.remove(path)
+    return weights, np.load(GOLDEN)
+
+
+@pytest.mark.parametrize("count", [1, 2])
+def test_the_session_with_attention_tracks_the_reference_block(loaded, count):
+    weights, golden = loaded
+    assert weights.dims == session.ModelDims() and weights.layers == block_case.LAYERS
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, block_case.TOKENS, count)
+    s.set_attention(True)
+    x = torch.from_numpy(golden["x"].copy()).view(torch.bfloat16)
+    s.run(stream, x, torch.from_numpy(golden["mods"][:count].copy()), torch.from_numpy(golden["cos"]),
+          torch.from_numpy(golden["sin"]))
+    got = x.view(torch.int16).numpy().view(np.uint16)
+    want = golden[f"after_block_{count - 1}"]
+    rel = session_oracle.relative_l2(got, want)
+    print(f"CUDA session vs Krea2Ref, {count} block(s): relative RMS {rel:.5f} (reference kernels vs the same code "
+          f"over 28 blocks: 0.0117)")
+    assert rel < BOUNDS[count]
+    assert k.device_status() == 0
+    s.close()
