@@ -212,7 +212,11 @@ int krea2_quantized_forward(krea2_stream stream, size_t rows, const void *x, con
  *    krea2_quantized_static_workspace_bytes() (4 MiB; e.g. 64 rows of 6144 -> 6144, 16 rows of
  *    16384 -> 6144).  Larger calls are refused with KREA2_INVALID_ARGUMENT.
  *  - The first call on each device resolves the array's device address (with that device
- *    current); make that first call outside any stream capture.
+ *    current).  That lookup may make the CUDA runtime load the library's device image, which is
+ *    where the 4 MiB are reserved, so "allocates nothing" holds from the second call on: make the
+ *    first call per device at start-up, outside any stream capture.
+ *  - The stream and the buffers must belong to the device that is current in the calling
+ *    thread; a call that mixes devices is refused with KREA2_INVALID_ARGUMENT.
  *  - All calls on a device share the one array and it keeps the previous call's bytes.  Every
  *    byte that is read is written earlier in the same call, so nothing needs clearing; but two
  *    calls that overlap on the GPU (different streams, or graph branches) race on it. */

@@ -103,6 +103,23 @@ extern "C" int krea2_quantized_forward_static(krea2_stream stream, size_t rows, 
     int device = 0;
     KREA2_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(KREA2_INTERNAL, "device index %d out of range", device);
+    // The array handed to the kernels is the current device's: a stream or buffers of another device would
+    // make that device's kernels dereference an address that is not mapped there.
+    if (stream) {
+        int stream_device = device;
+        if (cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &stream_device) != cudaSuccess) {
+            cudaGetLastError();  // a driver without the query: the buffer check below still applies
+            stream_device = device;
+        }
+        KREA2_REQUIRE(stream_device == device,
+                      "quantized_forward_static: the stream belongs to device %d but device %d is current", stream_device,
+                      device);
+    }
+    cudaPointerAttributes where{};
+    if (cudaPointerGetAttributes(&where, x) != cudaSuccess) cudaGetLastError();
+    else
+        KREA2_REQUIRE(where.type != cudaMemoryTypeDevice || where.device == device,
+                      "quantized_forward_static: x lives on device %d but device %d is current", where.device, device);
     uint8_t *workspace = nullptr;
     {
         std::lock_guard<std::mutex> guard(lock);

@@ -246,9 +246,11 @@ int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *
                    krea2_rope_qknorm_f16(stream, t, s->fused, w.qnorm, w.knorm, s->cos, s->sin, s->q, s->k, s->v, s->qkvg,
                                          q_heads, d.kv_heads, hidden, 1e-5f))
         KREA2_STEP("V transpose", krea2_v_transpose(stream, t, s->v, s->v_transposed, kv_width, s->capacity))
-        KREA2_STEP("f16 attention",
-                   krea2_attention_gqa_lds_f16_wmma(stream, t, d.kv_heads, s->q, s->k, s->v_transposed, s->attn_gu, hidden,
-                                                    kv_width, hidden, s->capacity, 0.08838834764831845f))
+        // shape::attention_source (src/kernels/shape.rs:24-31): the 32-query-row export from 8192 tokens on
+        auto attention = krea2_shape_attention_rows(t) == 32 ? krea2_attention_gqa_lds_f16_wmma_q32
+                                                             : krea2_attention_gqa_lds_f16_wmma;
+        KREA2_STEP("f16 attention", attention(stream, t, d.kv_heads, s->q, s->k, s->v_transposed, s->attn_gu, hidden, kv_width,
+                                              hidden, s->capacity, 0.08838834764831845f))
         KREA2_STEP("prepare gated", krea2_prepare_gated_i8(stream, t, s->attn_gu, s->fused + s->gate_offset * 2, s->a_q,
                                                            s->a_s, hidden, ph, s->qkvg))
     } else {
@@ -457,6 +459,10 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     if (int status = krea2_session_validate_dimensions(tokens, layers)) return status;
     KREA2_REQUIRE(weights && out, "session_create: null argument");
     KREA2_REQUIRE(layers <= weights->layers, "the weights hold %zu blocks, %zu were asked for", weights->layers, layers);
+    int current_device = 0;
+    KREA2_CUDA(cudaGetDevice(&current_device));
+    KREA2_REQUIRE(current_device == weights->device, "the weights live on device %d but device %d is current",
+                  weights->device, current_device);
     if (int status = prepare_gemm_device()) return status;
     if (int status = prepare_attention_device()) return status;
     if (int status = prepare_prologue_device(static_cast<cudaStream_t>(stream))) return status;

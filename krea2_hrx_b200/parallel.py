@@ -169,7 +169,7 @@ class TensorParallel:
         self.flags = fabric.allocate("flags", rank, (8,), torch.int32)
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.epoch_base = torch.zeros(1, dtype=torch.int32, device="cuda")  # advanced once per forward
-        self.graph = None
+        self.graphs = {}  # collective -> recorded CUDA graph
         self.a_q = torch.zeros((cap, shape.gemm_pitch(wide)), dtype=torch.int8, device="cuda")
         self.a_s = torch.zeros(cap, dtype=torch.float32, device="cuda")
         self.epoch = 0
@@ -223,6 +223,12 @@ class TensorParallel:
         from . import ops
         d, t, st = self.dims, self.tokens, self.stream
         h, inter, qkvg = d.hidden, d.inter, d.qkvg
+        # torch's own copies and collectives between the launches must be queued on the same stream as the
+        # launches: the generator holds that stream current across its yields
+        with torch.cuda.stream(st):
+            yield from self._stages(mods, collective, ops, d, t, st, h, inter, qkvg)
+
+    def _stages(self, mods, collective, ops, d, t, st, h, inter, qkvg) -> Iterator[None]:
 
         def after_gemm(name, n_total, swiglu=False):
             if collective == "fused":
@@ -256,32 +262,52 @@ class TensorParallel:
         if collective == "fused":
             check(lib().krea2_shard_advance(st.cuda_stream, self.epoch_base.data_ptr(), self.epoch))
 
-    def forward(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused") -> torch.Tensor:
-        """x: device bf16 [tokens][hidden] (the same on every rank); returns the new residual stream."""
-        self.x[: self.tokens].copy_(x)
+    def _checked(self, check_status: bool) -> None:
+        if check_status:
+            from ._lib import Runtime, device_status
+            status = device_status()  # synchronises the device
+            if status != 0:
+                raise Runtime(f"device status {status}: a bounded wait of the sharded chain ran out (bit 16: a peer's "
+                              "slab never arrived); the result is not valid")
+
+    def forward(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused", check: bool = False) -> torch.Tensor:
+        """x: device bf16 [tokens][hidden] (the same on every rank); returns the new residual stream.
+
+        The waits for the peers' slabs are bounded (two seconds): when one runs out -- a peer that died, or one
+        that is merely slow, e.g. still loading its module or instantiating its graph -- the device status word is
+        raised and the chain CONTINUES on whatever has arrived.  The result is therefore valid only if
+        `krea2_hrx_b200.device_status()` reads 0 afterwards; `check=True` reads it here (which synchronises the
+        device) and raises `Runtime` otherwise."""
+        with torch.cuda.stream(self.stream):
+            self.x[: self.tokens].copy_(x)
         for _ in self.stages(mods, collective):
             pass
+        self._checked(check)
         return self.x[: self.tokens]
 
-    def forward_graph(self, x: torch.Tensor, mods: torch.Tensor) -> torch.Tensor:
-        """The fused forward replayed from a CUDA graph recorded on first use (the inputs are copied
-        into fixed buffers, as Session.run_device does).  Every rank must call it the same number of
-        times: the flags count forwards."""
-        if self.graph is None:
-            self._mods = mods.clone()
+    def forward_graph(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused", check: bool = False) -> torch.Tensor:
+        """The forward replayed from a CUDA graph recorded on first use (the inputs are copied into fixed buffers,
+        as Session.run_device does); one graph per `collective`.  Every rank must call it the same number of times:
+        the flags count forwards.  As with `forward`, the result is valid only if the device status reads 0
+        afterwards (`check=True` reads it, synchronising the device)."""
+        if collective not in self.graphs:
+            if not hasattr(self, "_mods"):
+                self._mods = mods.clone()
             capture = torch.cuda.Stream()
-            capture.wait_stream(torch.cuda.current_stream())
+            capture.wait_stream(self.stream)
             saved = self.stream
             self.stream = capture
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=capture):
-                for _ in self.stages(self._mods, "fused"):
+                for _ in self.stages(self._mods, collective):
                     pass
             self.stream = saved
-            self.graph = graph
-        self._mods.copy_(mods)
-        self.x[: self.tokens].copy_(x)
-        self.graph.replay()
+            self.graphs[collective] = graph
+        with torch.cuda.stream(self.stream):
+            self._mods.copy_(mods)
+            self.x[: self.tokens].copy_(x)
+            self.graphs[collective].replay()
+        self._checked(check)
         return self.x[: self.tokens]
 
 

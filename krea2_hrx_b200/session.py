@@ -165,9 +165,20 @@ class Session:
                                       cos.data_ptr(), sin.data_ptr(), first_block, block_count or 0))
 
     def run_device(self, stream, x: torch.Tensor, mods: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
-        """Session::run_device (mod.rs:553-588): DEVICE x and mods, graph replay, asynchronous."""
-        if cos.numel() != self.tokens() * self.weights.dims.head_dim or sin.numel() != cos.numel():
+        """Session::run_device (mod.rs:553-588): DEVICE x (bf16 [tokens][hidden], updated in place) and mods (f32
+        [layers][6][hidden]), HOST cos/sin (f32 [tokens][head_dim]; the library fingerprints them on the host and
+        uploads them only when they change); graph replay, asynchronous."""
+        dims = self.weights.dims
+        for t in (cos, sin):
+            if t.is_cuda or not t.is_contiguous() or t.dtype != torch.float32:
+                raise InvalidArgument("Session.run_device takes cos/sin as contiguous float32 host tensors")
+        if cos.numel() != self.tokens() * dims.head_dim or sin.numel() != cos.numel():
             raise InvalidArgument("cos/sin have the wrong element count")
+        if not x.is_cuda or not x.is_contiguous() or x.dtype != torch.bfloat16 or x.numel() != self.tokens() * dims.hidden:
+            raise InvalidArgument("Session.run_device takes x as a contiguous CUDA bfloat16 [tokens][hidden] tensor")
+        if not mods.is_cuda or not mods.is_contiguous() or mods.dtype != torch.float32 \
+                or mods.numel() != self.layers() * 6 * dims.hidden:
+            raise InvalidArgument("Session.run_device takes mods as a contiguous CUDA float32 [layers][6][hidden] tensor")
         check(lib().krea2_session_run_device(self._handle, (stream or self.stream).cuda_stream, x.data_ptr(),
                                              x.numel() * x.element_size(), mods.data_ptr(),
                                              mods.numel() * mods.element_size(), cos.data_ptr(), sin.data_ptr()))

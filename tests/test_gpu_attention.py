@@ -165,6 +165,34 @@ def test_attention_at_the_session_shape_on_sampled_rows(ops):
     kat.close(kat.f16_from_bits(bits(out[rows])).astype(np.float64), want, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("tokens", [8192, 8219, 16896])
+def test_long_sequences_through_the_q32_export_on_sampled_rows(ops, tokens):
+    """The reference switches to its 32-query-row kernel at 8192 tokens (src/kernels/shape.rs:20-31) and serves up
+    to 16896 (:8).  The session shape, 48 query heads over 12 key/value heads, through the `_q32` export: sampled
+    query rows (first, last, both sides of the 128-key tiles and of the 256 query rows a block owns) against
+    float64, and the plain export must give the same bytes."""
+    from krea2_hrx_b200 import shape
+    assert shape.attention_rows(tokens) == 32
+    qh, kvh = 48, 12
+    capacity = shape.capacity(tokens)
+    gen = torch.Generator(device="cuda").manual_seed(tokens)
+    q = (torch.randn((tokens, qh * 128), generator=gen, device="cuda") * 1.2).to(torch.float16)
+    kk = (torch.randn((tokens, kvh * 128), generator=gen, device="cuda") * 1.2).to(torch.float16)
+    kk[tokens // 3:] *= 1.5  # later keys score higher: the running maximum moves
+    v = torch.randn((tokens, kvh * 128), generator=gen, device="cuda").to(torch.float16)
+    vt = torch.zeros((kvh * 128, capacity), dtype=torch.float16, device="cuda")
+    ops.v_transpose(v, vt, kvh * 128, capacity)
+    scale = 1.0 / np.sqrt(128)
+    out = torch.zeros((tokens, qh * 128), dtype=torch.float16, device="cuda")
+    ops.attention_gqa(tokens, kvh, q, kk, vt, out, qh * 128, kvh * 128, qh * 128, capacity, scale, q32=True)
+    rows = [0, 255, 256, tokens // 2 - 1, 8191, tokens - 129, tokens - 1]
+    want = oracle.attention_gqa(bits(q[rows]), bits(kk), bits(v), qh, kvh, scale)
+    kat.close(kat.f16_from_bits(bits(out[rows])).astype(np.float64), want, 2e-2, 2e-2)
+    plain = torch.zeros_like(out)
+    ops.attention_gqa(tokens, kvh, q, kk, vt, plain, qh * 128, kvh * 128, qh * 128, capacity, scale)
+    assert torch.equal(plain.view(torch.int16), out.view(torch.int16))
+
+
 def test_attention_repeated_dispatch_is_deterministic(ops):
     """The reference's race check (tests/softmax_repeat.rs) for the attention kernel: the same launch, repeated
     while other work keeps the device busy, gives the same bytes every time.  The kernel orders its products
