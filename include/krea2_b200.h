@@ -187,6 +187,44 @@ int krea2_shard_wait(krea2_stream stream, const uint32_t *flags, uint32_t world,
                      const uint32_t *epoch_base);
 int krea2_shard_advance(krea2_stream stream, uint32_t *epoch_base, uint32_t delta);
 
+/* ---------------------------------------------------------------- token-sharded blocks
+ * New with this library.  Every prologue, GEMM row and query row of a block belongs to one token, so with the
+ * weights replicated device r can run rows [first_row, first_row + tokens) of the sequence through the whole
+ * block alone; the one thing a token needs from the others is their keys and values.  The sharded QK-norm +
+ * RoPE launch therefore stores its K and V rows into EVERY device's full-length K and V tensors through
+ * peer-mapped pointers (the all-gather rides in the kernel's own stores over NVLink) and publishes `epoch` in
+ * slot `rank` of every device's flag array when its last block has finished; krea2_shard_wait holds a stream
+ * until all `world` slots have arrived, and the attention launch then takes this device's query rows against
+ * all keys.  Per block that moves 2 * tokens * kv_heads * 128 f16 values per device instead of the column-sharded
+ * chain's full activations.  Results are bit-identical to the single-device block. */
+typedef struct krea2_row_shard {
+    uint32_t world;     /* devices, 1..8 */
+    uint32_t rank;      /* this device's flag slot */
+    void *k_dest[8];    /* every device's K tensor, f16 [all tokens][kv_heads * 128] */
+    void *v_dest[8];    /* every device's V tensor, same shape */
+    size_t first_row;   /* row of the full sequence that this launch's first token is */
+    uint32_t *flags[8]; /* per device, `world` u32 slots; NULL entries are not signalled */
+    uint32_t epoch;     /* value published when this launch's stores are complete */
+    uint32_t *counter;  /* u32 on this device, zero before the first launch (the kernel re-zeroes it) */
+    const uint32_t *epoch_base; /* optional device word added to `epoch` (see krea2_shard) */
+} krea2_row_shard;
+
+/* krea2_rope_qknorm_f16 on this device's rows: q_out holds the local rows, K and V go to the shard's
+ * destinations at row first_row + local row; cos/sin are the local rows' tables. */
+int krea2_rope_qknorm_f16_sharded(krea2_stream stream, size_t tokens, const void *qkv, const float *q_scale,
+                                  const float *k_scale, const float *cos_table, const float *sin_table, void *q_out,
+                                  size_t row_stride, size_t q_heads, size_t kv_heads, size_t k_offset, float eps,
+                                  const krea2_row_shard *shard);
+/* Publishes the shard's epoch in every device's flag slot once the stream's earlier work has finished (no
+ * rows are stored; k_dest / v_dest / first_row / counter are ignored): the fence that ends a sharded forward,
+ * after which no device still reads what the next forward's launches overwrite. */
+int krea2_shard_signal(krea2_stream stream, const krea2_row_shard *shard);
+/* Grouped-query attention of `q_rows` query rows (q and out hold just those rows) against all `tokens` keys
+ * and values: krea2_attention_gqa_lds_f16_wmma is this call with q_rows = tokens. */
+int krea2_attention_gqa_f16_rows(krea2_stream stream, size_t q_rows, size_t tokens, size_t kv_heads, const void *q,
+                                 const void *k, const void *v_transposed, void *out, size_t q_stride, size_t kv_stride,
+                                 size_t out_stride, size_t token_capacity, float scale);
+
 /* bf16 <-> f16 transport of src/training/quantized.rs:63-72,102-110 (`lora_transport`,
  * reverse = 1: bf16 -> f16, reverse = 2: f16 -> bf16). */
 int krea2_lora_transport(krea2_stream stream, size_t elements, const void *src, void *dst, int reverse);

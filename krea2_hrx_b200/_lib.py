@@ -54,6 +54,12 @@ class Shard(ctypes.Structure):
                 ("offset", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p), ("epoch_base", c_void_p)]
 
 
+class RowShard(ctypes.Structure):
+    _fields_ = [("world", c_uint32), ("rank", c_uint32), ("k_dest", c_void_p * 8), ("v_dest", c_void_p * 8),
+                ("first_row", c_size_t), ("flags", c_void_p * 8), ("epoch", c_uint32), ("counter", c_void_p),
+                ("epoch_base", c_void_p)]
+
+
 class SpanInfo(ctypes.Structure):
     _fields_ = [(name, c_size_t) for name in ("device_offset", "device_bytes", "rows", "row_bytes",
                                                "device_row_bytes", "segments", "file_bytes")]
@@ -96,6 +102,11 @@ SIGNATURES = {
     "krea2_gemm_i8_sharded": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                       c_size_t, c_size_t, POINTER(Shard)]),
     "krea2_shard_wait": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "krea2_rope_qknorm_f16_sharded": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_size_t, c_size_t, c_size_t, c_size_t, c_float, POINTER(RowShard)]),
+    "krea2_shard_signal": (c_int, [c_void_p, POINTER(RowShard)]),
+    "krea2_attention_gqa_f16_rows": (c_int, [c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
     "krea2_shard_advance": (c_int, [c_void_p, c_void_p, c_uint32]),
     "krea2_lora_transport": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int]),
     "krea2_quantized_workspace_bytes": (c_size_t, [c_size_t, c_size_t, c_size_t]),

@@ -32,13 +32,38 @@ constexpr unsigned kFull = 0xffffffffu;
 // One 256-thread block per token, a warp per head, four channels per lane
 // (kernels/rope_qknorm_f16.loom:78-157).  The two sums the reference leaves unordered are fixed
 // as ((s0+s1)+(s2+s3)) per lane and the xor butterfly 16..1 across the warp; rsqrt is 1/sqrt.
+// Token-sharded launches (template flag S): this device computes rows first_row.. of the sequence and stores
+// its K and V rows into EVERY device's full-length K and V tensors through peer-mapped pointers, so the
+// all-gather of keys and values rides in this kernel's own stores over NVLink.  When the last block has
+// finished, slot `rank` of every device's flag array receives `epoch` (+ *epoch_base).
+struct RowPush {
+    uint32_t world, rank, first_row, epoch;
+    uint16_t *k_dest[8], *v_dest[8];
+    uint32_t *flags[8];
+    uint32_t *counter;
+    const uint32_t *epoch_base;
+};
+
+template <bool S>
+__device__ __forceinline__ void store_kv(const RowPush &push, uint16_t *const *dest, uint16_t *local, size_t at, uint2 value) {
+    if constexpr (S) {
+#pragma unroll
+        for (int d = 0; d < 8; d++)
+            if (d < static_cast<int>(push.world)) *reinterpret_cast<uint2 *>(dest[d] + at) = value;
+    } else {
+        *reinterpret_cast<uint2 *>(local + at) = value;
+    }
+}
+
+template <bool S>
 __global__ void __launch_bounds__(256)
 rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q_scale,
                    const float *__restrict__ k_scale, const float *__restrict__ cos_table,
                    const float *__restrict__ sin_table, uint16_t *__restrict__ q_out, uint16_t *__restrict__ k_out,
                    uint16_t *__restrict__ v_out, uint32_t row_stride, uint32_t q_heads, uint32_t kv_heads,
-                   uint32_t k_offset, float eps) {
+                   uint32_t k_offset, float eps, const RowPush push) {
     const size_t row = blockIdx.x;
+    const size_t kv_row = S ? row + push.first_row : row;  // the row of the full-length K and V tensors
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = lane * 4;
     const uint32_t heads_total = q_heads + 2 * kv_heads;
     const float4 cs = __ldg(reinterpret_cast<const float4 *>(cos_table + row * 128 + col));
@@ -63,7 +88,7 @@ rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q
             const uint2 raw = raws[b];
             const bool is_q = head < q_heads, is_v = head >= q_heads + kv_heads;
             if (is_v) {
-                *reinterpret_cast<uint2 *>(v_out + row * (kv_heads * 128) + (head - q_heads - kv_heads) * 128 + col) = raw;
+                store_kv<S>(push, push.v_dest, v_out, kv_row * (kv_heads * 128) + (head - q_heads - kv_heads) * 128 + col, raw);
                 continue;
             }
             const __half2 lo = *reinterpret_cast<const __half2 *>(&raw.x), hi = *reinterpret_cast<const __half2 *>(&raw.y);
@@ -86,10 +111,42 @@ rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q
             uint2 packed;
             packed.x = *reinterpret_cast<const uint32_t *>(&out_lo);
             packed.y = *reinterpret_cast<const uint32_t *>(&out_hi);
-            uint16_t *dst = is_q ? q_out + row * (q_heads * 128) + head * 128 : k_out + row * (kv_heads * 128) + (head - q_heads) * 128;
-            *reinterpret_cast<uint2 *>(dst + col) = packed;
+            if (is_q)
+                *reinterpret_cast<uint2 *>(q_out + row * (q_heads * 128) + head * 128 + col) = packed;
+            else
+                store_kv<S>(push, push.k_dest, k_out, kv_row * (kv_heads * 128) + (head - q_heads) * 128 + col, packed);
         }
     }
+    if constexpr (S) {
+        // Every storing thread fences at system scope; the last block to finish publishes the epoch, so
+        // whoever observes the flag observes the rows.
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && push.counter != nullptr) {
+            const uint32_t finished = atomicAdd(push.counter, 1u);
+            if (finished == gridDim.x - 1) {
+                *push.counter = 0;  // ready for the next launch on this stream
+                const uint32_t value = push.epoch + (push.epoch_base ? *push.epoch_base : 0u);
+                __threadfence_system();
+#pragma unroll
+                for (int d = 0; d < 8; d++)
+                    if (d < static_cast<int>(push.world) && push.flags[d] != nullptr)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flags[d] + push.rank), "r"(value) : "memory");
+            }
+        }
+    }
+}
+
+// Publishes an epoch in slot `rank` of every device's flag array once everything queued before it on the
+// stream has finished: the fence a token-sharded forward ends with.
+__global__ void shard_signal_kernel(const RowPush push) {
+    if (threadIdx.x != 0) return;
+    const uint32_t value = push.epoch + (push.epoch_base ? *push.epoch_base : 0u);
+    __threadfence_system();
+#pragma unroll
+    for (int d = 0; d < 8; d++)
+        if (d < static_cast<int>(push.world) && push.flags[d] != nullptr)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flags[d] + push.rank), "r"(value) : "memory");
 }
 
 // ---------------------------------------------------------------- v transpose
@@ -273,7 +330,9 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
 constexpr uint32_t kIdescF16 = (1u << 4) | (static_cast<uint32_t>(kTile >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
 
 struct AttnArgs {
-    uint32_t tokens, q_heads_per_kv, out_stride;
+    uint32_t tokens;  // keys and values
+    uint32_t q_rows;  // query rows of this launch (= tokens unless the rows are sharded over devices)
+    uint32_t q_heads_per_kv, out_stride;
     float scale_log2;  // softmax scale times log2(e)
     uint16_t *out;
 };
@@ -517,7 +576,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int c = 0; c < 4; c++) {
                 float o[32];
                 tmem_load_32(o_addr + c * 32, o);
-                if (row < g.tokens) {
+                if (row < g.q_rows) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         uint32_t w[4];
@@ -631,11 +690,70 @@ extern "C" int krea2_rope_qknorm_f16(krea2_stream stream, size_t tokens, const v
     KREA2_REQUIRE(aligned16(qkv) && aligned16(q_scale) && aligned16(k_scale) && aligned16(cos_table) && aligned16(sin_table) &&
                       aligned16(q_out) && aligned16(k_out) && aligned16(v_out),
                   "rope_qknorm_f16: buffers must be 16-byte aligned");
-    rope_qknorm_kernel<<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    rope_qknorm_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t *>(qkv), q_scale, k_scale, cos_table, sin_table, static_cast<uint16_t *>(q_out),
         static_cast<uint16_t *>(k_out), static_cast<uint16_t *>(v_out), static_cast<uint32_t>(row_stride),
-        static_cast<uint32_t>(q_heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(k_offset), eps);
+        static_cast<uint32_t>(q_heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(k_offset), eps, RowPush{});
     return launch_check("rope_qknorm_f16");
+}
+
+namespace {
+int fill_push(const char *name, const krea2_row_shard *shard, bool with_rows, RowPush *push) {
+    KREA2_REQUIRE(shard, "%s: shard description is null", name);
+    KREA2_REQUIRE(shard->world >= 1 && shard->world <= 8 && shard->rank < shard->world, "%s: world %u / rank %u outside 1..8",
+                  name, shard->world, shard->rank);
+    KREA2_REQUIRE(shard->first_row <= 0xffffffffull, "%s: first_row too large", name);
+    *push = RowPush{};
+    push->world = shard->world, push->rank = shard->rank, push->first_row = static_cast<uint32_t>(shard->first_row);
+    push->epoch = shard->epoch, push->counter = shard->counter, push->epoch_base = shard->epoch_base;
+    bool any_flag = false;
+    for (uint32_t d = 0; d < shard->world; d++) {
+        if (with_rows)
+            KREA2_REQUIRE(shard->k_dest[d] && shard->v_dest[d] && aligned16(shard->k_dest[d]) && aligned16(shard->v_dest[d]),
+                          "%s: destination %u is null or unaligned", name, d);
+        push->k_dest[d] = static_cast<uint16_t *>(shard->k_dest[d]);
+        push->v_dest[d] = static_cast<uint16_t *>(shard->v_dest[d]);
+        push->flags[d] = shard->flags[d];
+        any_flag = any_flag || shard->flags[d] != nullptr;
+    }
+    KREA2_REQUIRE(!with_rows || !any_flag || shard->counter, "%s: flags need the launch counter", name);
+    return KREA2_OK;
+}
+}  // namespace
+
+extern "C" int krea2_rope_qknorm_f16_sharded(krea2_stream stream, size_t tokens, const void *qkv, const float *q_scale,
+                                             const float *k_scale, const float *cos_table, const float *sin_table,
+                                             void *q_out, size_t row_stride, size_t q_heads, size_t kv_heads,
+                                             size_t k_offset, float eps, const krea2_row_shard *shard) {
+    clear_error();
+    KREA2_REQUIRE(tokens >= 1 && tokens <= 1048576, "rope_qknorm_f16_sharded: tokens %zu outside 1..1048576", tokens);
+    KREA2_REQUIRE(row_stride >= 128 && row_stride <= 65536 && row_stride % 128 == 0,
+                  "rope_qknorm_f16_sharded: row_stride %zu must be a multiple of 128 up to 65536", row_stride);
+    KREA2_REQUIRE(q_heads >= 1 && q_heads <= 256 && kv_heads >= 1 && kv_heads <= 256,
+                  "rope_qknorm_f16_sharded: heads outside 1..256");
+    KREA2_REQUIRE(k_offset >= 128 && k_offset % 128 == 0 && k_offset >= q_heads * 128 &&
+                      k_offset + 2 * kv_heads * 128 <= row_stride,
+                  "rope_qknorm_f16_sharded: k_offset %zu must be a multiple of 128 past the q heads with k and v inside the row",
+                  k_offset);
+    KREA2_REQUIRE(qkv && q_scale && k_scale && cos_table && sin_table && q_out, "rope_qknorm_f16_sharded: null buffer");
+    KREA2_REQUIRE(aligned16(qkv) && aligned16(q_scale) && aligned16(k_scale) && aligned16(cos_table) && aligned16(sin_table) &&
+                      aligned16(q_out),
+                  "rope_qknorm_f16_sharded: buffers must be 16-byte aligned");
+    RowPush push;
+    if (int status = fill_push("rope_qknorm_f16_sharded", shard, true, &push)) return status;
+    rope_qknorm_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(qkv), q_scale, k_scale, cos_table, sin_table, static_cast<uint16_t *>(q_out), nullptr,
+        nullptr, static_cast<uint32_t>(row_stride), static_cast<uint32_t>(q_heads), static_cast<uint32_t>(kv_heads),
+        static_cast<uint32_t>(k_offset), eps, push);
+    return launch_check("rope_qknorm_f16_sharded");
+}
+
+extern "C" int krea2_shard_signal(krea2_stream stream, const krea2_row_shard *shard) {
+    clear_error();
+    RowPush push;
+    if (int status = fill_push("shard_signal", shard, false, &push)) return status;
+    shard_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(push);
+    return launch_check("shard_signal");
 }
 
 extern "C" int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x, void *out, size_t width,
@@ -653,11 +771,12 @@ extern "C" int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x
     return launch_check("v_transpose");
 }
 
-extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
-                                                const void *k, const void *v_transposed, void *out, size_t q_stride,
-                                                size_t kv_stride, size_t out_stride, size_t token_capacity, float scale) {
+extern "C" int krea2_attention_gqa_f16_rows(krea2_stream stream, size_t q_rows, size_t tokens, size_t kv_heads, const void *q,
+                                            const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                            size_t kv_stride, size_t out_stride, size_t token_capacity, float scale) {
     clear_error();
     KREA2_REQUIRE(tokens >= 16 && tokens <= 65536, "attention: tokens %zu outside 16..65536", tokens);
+    KREA2_REQUIRE(q_rows >= 1 && q_rows <= tokens, "attention: q_rows %zu outside 1..tokens", q_rows);
     KREA2_REQUIRE(q_stride >= 128 && q_stride <= 32768 && q_stride % 128 == 0 && kv_stride >= 128 && kv_stride <= 32768 &&
                       kv_stride % 128 == 0 && out_stride >= 128 && out_stride <= 32768 && out_stride % 128 == 0,
                   "attention: strides must be multiples of 128 up to 32768");
@@ -672,18 +791,26 @@ extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t toke
                   "attention: buffers must be non-null and 16-byte aligned");
     if (int status = ensure_attention()) return status;
     CUtensorMap map_q, map_k, map_v;
-    if (int status = make_f16_map(&map_q, q, q_stride, tokens, q_stride)) return status;
+    if (int status = make_f16_map(&map_q, q, q_stride, q_rows, q_stride)) return status;
     if (int status = make_f16_map(&map_k, k, kv_stride, tokens, kv_stride)) return status;
     if (int status = make_f16_map(&map_v, v_transposed, token_capacity, kv_stride, token_capacity)) return status;
     AttnArgs args;
     args.tokens = static_cast<uint32_t>(tokens);
+    args.q_rows = static_cast<uint32_t>(q_rows);
     args.q_heads_per_kv = static_cast<uint32_t>(q_stride / kv_stride);
     args.out_stride = static_cast<uint32_t>(out_stride);
     args.scale_log2 = scale * 1.4426950408889634f;
     args.out = static_cast<uint16_t *>(out);
-    dim3 grid(static_cast<unsigned>((tokens + 2 * kTile - 1) / (2 * kTile)), static_cast<unsigned>(q_stride / 128), 1);
+    dim3 grid(static_cast<unsigned>((q_rows + 2 * kTile - 1) / (2 * kTile)), static_cast<unsigned>(q_stride / 128), 1);
     attention_kernel<<<grid, kAttnThreads, kAttnSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, args);
     return launch_check("attention");
+}
+
+extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,
+                                                const void *k, const void *v_transposed, void *out, size_t q_stride,
+                                                size_t kv_stride, size_t out_stride, size_t token_capacity, float scale) {
+    return krea2_attention_gqa_f16_rows(stream, tokens, tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride,
+                                        out_stride, token_capacity, scale);
 }
 
 extern "C" int krea2_attention_gqa_lds_f16_wmma_q32(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,

@@ -94,6 +94,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         }
     }
 }
+// Accounts for `bytes` of a transaction that will never arrive (teardown only).
+__device__ __forceinline__ void mbar_complete_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Teardown after an abort: waits (bounded) for the given phase of a stage's `full` barrier, i.e. until the
+// loads armed on it have landed; a wait that runs out is recorded in the status word.
+__device__ __forceinline__ void drain_stage(uint64_t *bar, uint32_t parity, uint64_t start) {
+    while (!mbar_try_wait(bar, parity)) {
+        if (global_timer_ns() - start > kWaitLimitNs) {
+            atomicOr(&g_device_status, kDrainTimedOut);
+            return;
+        }
+    }
+}
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -151,6 +165,9 @@ __device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank) {
     uint32_t out;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
     return out;
+}
+__device__ __forceinline__ void store_cluster_u32(uint32_t cluster_address, uint32_t value) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_address), "r"(value) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -440,6 +457,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
     const uint32_t tiles = m_tiles * (g.n / BN);
+    uint32_t armed = 0, armed_parity = 0;  // producer thread: stages with a load issued, and the phase of the last one
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < T::kStages; s++) {
@@ -465,7 +483,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == kProducerWarp) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            uint32_t stage = 0, phase = 0;
             bool alive = true;
             for (uint32_t tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x) {
                 const int m0 = static_cast<int>(tile % m_tiles) * kBlockM;
@@ -484,19 +502,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (++stage == T::kStages) {
                         stage = 0;
                         phase ^= 1u;
-                    }
-                }
-            }
-            if (*abort_flag) {
-                // Drain: no load of this CTA may still be writing shared memory when it exits.
-                const uint64_t start = global_timer_ns();
-                for (int s = 0; s < T::kStages; s++) {
-                    if (!(armed & (1u << s))) continue;
-                    while (!mbar_try_wait(full + s, (armed_parity >> s) & 1u)) {
-                        if (global_timer_ns() - start > kWaitLimitNs) {
-                            atomicOr(&g_device_status, kDrainTimedOut);
-                            break;
-                        }
                     }
                 }
             }
@@ -557,8 +562,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();  // every role is done: the abort flag is final
     tc_fence_after();
+    if (*abort_flag) {
+        // Drain: no load of this CTA may still be writing shared memory when it exits.  Whichever role gave
+        // up, the producer thread waits here for the last load it issued into every stage.
+        if (warp == kProducerWarp && lane == 0) {
+            const uint64_t start = global_timer_ns();
+            for (int s = 0; s < T::kStages; s++)
+                if (armed & (1u << s)) drain_stage(full + s, (armed_parity >> s) & 1u, start);
+        }
+        __syncthreads();
+    }
     if (warp == kMmaWarp) {
         __syncwarp();
         tmem_dealloc(tmem_base, T::kTmemColumns);
@@ -599,10 +614,14 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    // Teardown exchange: [0], [1] the loads each CTA's producer issued (kept in the leader), [2], [3] each CTA's
+    // abort flag (kept in both CTAs).
+    volatile uint32_t *exchange = reinterpret_cast<volatile uint32_t *>(tmem_slot + 2);
     uint8_t *staging = smem + T::kStages * T::kStageBytes + 256;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
+    uint32_t issued = 0;  // producer thread: stage loads issued by this CTA
     const bool leader = rank == 0;
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t m_tiles = (g.m + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -665,16 +684,11 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (leader) mbar_expect_tx(full + stage, 2 * T::kStageBytes);
                     tma_load_2d_pair(a_dst, &map_a, leader_full, static_cast<int>(kb) * kBlockK, m0);
                     tma_load_2d_pair(a_dst + T::kABytes, &map_w, leader_full, static_cast<int>(kb) * kBlockK, n0);
+                    issued++;
                     if (++stage == T::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
-                }
-            }
-            if (*abort_flag) {
-                // Give loads still in flight time to land before this CTA can exit.
-                const uint64_t start = global_timer_ns();
-                while (global_timer_ns() - start < 200000ull) {
                 }
             }
         }
@@ -733,8 +747,38 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 
     tc_fence_before();
+    __syncthreads();  // every role of this CTA is done: its abort flag is final
+    if (threadIdx.x == 0) {
+        const uint32_t mine = *abort_flag ? 1u : 0u;
+        store_cluster_u32(map_to_cta(const_cast<uint32_t *>(exchange) + 2 + rank, 0), mine);
+        store_cluster_u32(map_to_cta(const_cast<uint32_t *>(exchange) + 2 + rank, 1), mine);
+    }
+    if (warp == kProducerWarp && lane == 0) store_cluster_u32(map_to_cta(const_cast<uint32_t *>(exchange) + rank, 0), issued);
+    __syncwarp();
     cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still use it
     tc_fence_after();
+    if (exchange[2] | exchange[3]) {
+        // One of the CTAs gave up on a wait.  No load may still be writing either CTA's shared memory when the
+        // cluster exits, and every load of the pair completes on the LEADER's `full` barriers: the leader's
+        // producer thread waits for the last load into every stage.  Where only one CTA issued that load (they
+        // can be up to a ring apart when a wait runs out) the barrier's byte count is first put right: the
+        // peer's missing half is accounted as complete, or the peer's lone half is armed.
+        if (leader && warp == kProducerWarp && lane == 0) {
+            const uint32_t issued_leader = exchange[0], issued_peer = exchange[1];
+            const uint32_t high = issued_leader > issued_peer ? issued_leader : issued_peer;
+            const uint32_t low = high > static_cast<uint32_t>(T::kStages) ? high - T::kStages : 0u;
+            const uint64_t start = global_timer_ns();
+            for (uint32_t i = low; i < high; i++) {
+                const uint32_t s = i % T::kStages, parity = (i / T::kStages) & 1u;
+                const bool by_leader = i < issued_leader, by_peer = i < issued_peer;
+                if (by_leader && !by_peer) mbar_complete_tx(full + s, T::kStageBytes);
+                if (!by_leader && by_peer) mbar_expect_tx(full + s, T::kStageBytes);
+                drain_stage(full + s, parity, start);
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();  // the peer stays until the leader has seen its loads land
+    }
     if (warp == kMmaWarp) {
         __syncwarp();
         tmem_dealloc_pair(tmem_base, T::kTmemColumns);

@@ -10,7 +10,9 @@
 // left out and the gated prologue reads the query columns of the fused buffer in place of an
 // attention output: the W8A8 chain alone, which the CPU oracle reproduces bit for bit.
 #include <atomic>
+#include <cerrno>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <memory>
 #include <string>
@@ -328,6 +330,14 @@ int run_profiled(krea2_session *s, size_t first, size_t count) {
     }
     KREA2_CUDA(cudaStreamSynchronize(s->stream));
     s->stages.clear();
+    // KREA2_PROFILE_JSON=FILE (src/session/mod.rs:438-459): the raw device intervals of this forward, appended
+    // as one JSON line.  Ticks are nanoseconds from the forward's first launch.
+    const char *json_path = getenv("KREA2_PROFILE_JSON");
+    std::string record;
+    if (json_path && *json_path)
+        record = "{\"tokens\":" + std::to_string(s->tokens) + ",\"layers\":" + std::to_string(count) +
+                 ",\"profile\":{\"frequency_hz\":1000000000,\"gaps_ms\":0.0,\"intervals\":[";
+    bool first_interval = true;
     for (size_t i = 0; i < count; i++)
         for (size_t k = 0; k < labels.size(); k++) {
             float ms = 0.0f;
@@ -336,7 +346,25 @@ int run_profiled(krea2_session *s, size_t first, size_t count) {
             for (auto &stage : s->stages)
                 if (std::string(stage.label) == labels[k]) stage.millis += ms, found = true;
             if (!found) s->stages.push_back(Stage{labels[k], ms});
+            if (!record.empty()) {
+                float begin_ms = 0.0f;
+                KREA2_CUDA(cudaEventElapsedTime(&begin_ms, s->events[0], s->events[i * per + k]));
+                const long long start_tick = static_cast<long long>(static_cast<double>(begin_ms) * 1e6 + 0.5);
+                const long long end_tick = start_tick + static_cast<long long>(static_cast<double>(ms) * 1e6 + 0.5);
+                record += std::string(first_interval ? "" : ",") + "{\"label\":\"" + labels[k] + "\",\"block\":" +
+                          std::to_string(first + i) + ",\"start_tick\":" + std::to_string(start_tick) + ",\"end_tick\":" +
+                          std::to_string(end_tick) + "}";
+                first_interval = false;
+            }
         }
+    if (!record.empty()) {
+        record += "]}}\n";
+        FILE *file = fopen(json_path, "a");
+        if (!file) return fail(KREA2_INVALID_ARGUMENT, "KREA2_PROFILE_JSON %s: %s", json_path, strerror(errno));
+        const bool written = fwrite(record.data(), 1, record.size(), file) == record.size();
+        if (fclose(file) != 0 || !written)
+            return fail(KREA2_INVALID_ARGUMENT, "KREA2_PROFILE_JSON %s: write failed", json_path);
+    }
     return KREA2_OK;
 }
 

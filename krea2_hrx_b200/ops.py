@@ -186,6 +186,27 @@ def attention_gqa(tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride
              out_stride, token_capacity, scale))
 
 
+def attention_gqa_rows(q_rows, tokens, kv_heads, q, k, v_transposed, out, q_stride, kv_stride, out_stride, token_capacity,
+                       scale, stream=None):
+    """`q_rows` query rows (q and out hold just those) against all `tokens` keys and values."""
+    check(lib().krea2_attention_gqa_f16_rows(_stream_ptr(stream), q_rows, tokens, kv_heads, _ptr(q), _ptr(k),
+                                             _ptr(v_transposed), _ptr(out), q_stride, kv_stride, out_stride,
+                                             token_capacity, scale))
+
+
+def rope_qknorm_f16_sharded(tokens, qkv, q_scale, k_scale, cos, sin, q_out, row_stride, q_heads, kv_heads, k_offset,
+                            shard, eps=1e-5, stream=None):
+    """QK-norm + RoPE of this device's rows; K and V rows go to every device's full-length tensors (`shard`:
+    a `_lib.RowShard`)."""
+    check(lib().krea2_rope_qknorm_f16_sharded(_stream_ptr(stream), tokens, qkv.data_ptr(), _ptr(q_scale), _ptr(k_scale),
+                                              _ptr(cos), _ptr(sin), _ptr(q_out), row_stride, q_heads, kv_heads, k_offset,
+                                              eps, ctypes.byref(shard)))
+
+
+def shard_signal(shard, stream=None):
+    check(lib().krea2_shard_signal(_stream_ptr(stream), ctypes.byref(shard)))
+
+
 # ------------------------------------------------------------------ around the block chain
 def modulation(vector, tables, out, stream=None):
     """Models::modulation (src/models/graph.rs:405-425): `out` f32 = bf16(vector[i % len] + tables[i])."""

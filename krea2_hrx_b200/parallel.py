@@ -1,6 +1,6 @@
 """Running the block chain on several GPUs.
 
-Two ways the W8A8 path spreads over devices, neither of which exists in the reference (one APU):
+Three ways the path spreads over devices, none of which exists in the reference (one APU):
 
 * data parallel over images -- one ordinary `session.Session` per device, no communication
   (`bench.py --gpus N`); nothing here is needed for it;
@@ -11,7 +11,13 @@ Two ways the W8A8 path spreads over devices, neither of which exists in the refe
   and launch, waited on by `krea2_shard_wait`, tells each device when every slab has landed.  No
   arithmetic changes, so the result is bit-identical to the single-device session.
   `TensorParallel.forward(..., collective="nccl")` is the baseline the fused path is compared with:
-  the same sharded GEMMs into local buffers, then an NCCL all-gather and a local repack.
+  the same sharded GEMMs into local buffers, then an NCCL all-gather and a local repack;
+* token-sharded rows within one image (`TokenParallel`): the weights are replicated and device r runs rows
+  [r*T/g, (r+1)*T/g) of the sequence through the whole block alone -- every prologue, GEMM row and query
+  row belongs to one token -- so the only exchange is the keys and values of each block, which the sharded
+  QK-norm + RoPE launch stores into every device's K and V tensors itself
+  (`krea2_rope_qknorm_f16_sharded`; `collective="nccl"` is the all-gather baseline).  Bit-identical to the
+  single-device block, attention included, at 1/15 of the column-sharded chain's bytes.
 """
 from __future__ import annotations
 
@@ -22,7 +28,7 @@ from typing import Iterator, List, Optional, Sequence, Tuple
 import torch
 
 from . import shape
-from ._lib import InvalidArgument, Shard, check, lib
+from ._lib import InvalidArgument, RowShard, Shard, check, lib
 from .session import ModelDims, Weights
 
 PLAIN, RESID, SWIGLU = 0, 1, 2
@@ -151,6 +157,16 @@ class SymmetricFabric:
         torch.cuda.synchronize()
 
 
+def require_clean_status() -> None:
+    """Reads the device status word (which synchronises the device) and raises `Runtime` when a bounded wait of a
+    sharded chain ran out, i.e. when the forward went on without a peer's data."""
+    from ._lib import Runtime, device_status
+    status = device_status()
+    if status != 0:
+        raise Runtime(f"device status {status}: a bounded wait of the sharded chain ran out (bit 16: a peer's data "
+                      "never arrived); the result is not valid")
+
+
 class TensorParallel:
     """One device's part of a column-sharded run of `layers` blocks over `tokens` rows."""
 
@@ -264,11 +280,7 @@ class TensorParallel:
 
     def _checked(self, check_status: bool) -> None:
         if check_status:
-            from ._lib import Runtime, device_status
-            status = device_status()  # synchronises the device
-            if status != 0:
-                raise Runtime(f"device status {status}: a bounded wait of the sharded chain ran out (bit 16: a peer's "
-                              "slab never arrived); the result is not valid")
+            require_clean_status()
 
     def forward(self, x: torch.Tensor, mods: torch.Tensor, collective: str = "fused", check: bool = False) -> torch.Tensor:
         """x: device bf16 [tokens][hidden] (the same on every rank); returns the new residual stream.
@@ -309,6 +321,195 @@ class TensorParallel:
             self.graphs[collective].replay()
         self._checked(check)
         return self.x[: self.tokens]
+
+
+def shard_rows(tokens: int, world: int) -> List[Tuple[int, int]]:
+    """(first row, rows) of each device's share of a sequence: equal shares of ceil(tokens / world) rows, the
+    last one shorter when the count does not divide."""
+    if world < 1 or world > 8:
+        raise InvalidArgument("world must be 1..8")
+    share = -(-tokens // world)
+    out = [(min(r * share, tokens), max(0, min(share, tokens - r * share))) for r in range(world)]
+    if any(count < 1 for _, count in out):
+        raise InvalidArgument(f"{tokens} rows do not give each of {world} devices a row")
+    return out
+
+
+class TokenParallel:
+    """One device's rows of a token-sharded run of `layers` full blocks (attention included) over `tokens` rows.
+
+    Cross-device ordering.  A device that has passed the wait of block i knows every peer has finished the
+    attention of block i - 1 (each peer's K/V stores of block i follow that attention in its stream), so K and V
+    alternate between two buffers by block parity and a device can run at most one block ahead of what its
+    peers still read.  A forward ends with a flag-only signal and wait, after which the next forward may reuse
+    both buffers.  The waits are bounded; as with `TensorParallel`, a result is valid only if
+    `krea2_hrx_b200.device_status()` reads 0 afterwards."""
+
+    SCALE = 0.08838834764831845  # 1 / sqrt(128), src/session/mod.rs:752
+
+    def __init__(self, fabric, rank: int, weights: Weights, tokens: int, layers: int,
+                 stream: Optional[torch.cuda.Stream] = None):
+        self.fabric, self.rank, self.world = fabric, rank, fabric.world
+        self.weights, self.dims, self.tokens, self.layers = weights, weights.dims, tokens, layers
+        self.stream = stream or torch.cuda.current_stream()
+        d = self.dims
+        if d.head_dim != 128:
+            raise InvalidArgument("the attention kernel is built for 128 channels per head")
+        self.rows = shard_rows(tokens, self.world)[rank]
+        self.share = -(-tokens // self.world)
+        first, count = self.rows
+        cap_local = shape.capacity(count)
+        self.cap = -(-max(shape.capacity(tokens), self.world * self.share) // 64) * 64
+        self.ph, self.pi = shape.gemm_pitch(d.hidden), shape.gemm_pitch(d.inter)
+        self.kv_width = d.kv_heads * d.head_dim
+        wide = max(d.hidden, d.inter)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.x = torch.zeros((cap_local, d.hidden), dtype=torch.bfloat16, device=dev)
+        self.a_q = torch.zeros((cap_local, shape.gemm_pitch(wide)), dtype=torch.int8, device=dev)
+        self.a_s = torch.zeros(cap_local, dtype=torch.float32, device=dev)
+        self.fused = torch.zeros((cap_local, d.qkvg), dtype=torch.float16, device=dev)
+        self.attn_gu = torch.zeros((cap_local, wide), dtype=torch.float16, device=dev)
+        self.q = torch.zeros((cap_local, d.hidden), dtype=torch.float16, device=dev)
+        self.k_local = torch.zeros((self.share, self.kv_width), dtype=torch.float16, device=dev)
+        self.v_local = torch.zeros((self.share, self.kv_width), dtype=torch.float16, device=dev)
+        self.vt = torch.zeros((self.kv_width, self.cap), dtype=torch.float16, device=dev)
+        self.k = [fabric.allocate(f"sp.k{b}", rank, (self.cap, self.kv_width), torch.float16) for b in range(2)]
+        self.v = [fabric.allocate(f"sp.v{b}", rank, (self.cap, self.kv_width), torch.float16) for b in range(2)]
+        self.flags = fabric.allocate("sp.flags", rank, (8,), torch.int32)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.cos = torch.zeros((count, d.head_dim), dtype=torch.float32, device=dev)
+        self.sin = torch.zeros((count, d.head_dim), dtype=torch.float32, device=dev)
+        self.mods = torch.zeros((layers, 6, d.hidden), dtype=torch.float32, device=dev)
+        self.epoch = 0
+        self.graphs = {}
+        self.blocks = []
+        for i in range(layers):
+            p = f"blocks.{i}"
+            block = {name: span_tensor(weights, f"{p}.{name}", torch.int8 if name.endswith(".q") else torch.float32)
+                     for name in ("qkvg.q", "qkvg.s", "wo.q", "wo.s", "gu.q", "gu.s", "down.q", "down.s", "prenorm",
+                                  "postnorm", "qnorm", "knorm")}
+            self.blocks.append(block)
+
+    def _shard(self, parity: Optional[int]) -> RowShard:
+        desc = RowShard()
+        desc.world, desc.rank, desc.first_row = self.world, self.rank, self.rows[0]
+        if parity is not None:
+            for r, ptr in enumerate(self.fabric.pointers(f"sp.k{parity}", self.rank)):
+                desc.k_dest[r] = ptr
+            for r, ptr in enumerate(self.fabric.pointers(f"sp.v{parity}", self.rank)):
+                desc.v_dest[r] = ptr
+        for r, ptr in enumerate(self.fabric.pointers("sp.flags", self.rank)):
+            desc.flags[r] = ptr
+        self.epoch += 1
+        desc.epoch = self.epoch
+        desc.counter = self.counter.data_ptr()
+        desc.epoch_base = self.epoch_base.data_ptr()
+        return desc
+
+    def _wait(self) -> None:
+        check(lib().krea2_shard_wait(self.stream.cuda_stream, self.flags.data_ptr(), self.world, self.epoch,
+                                     self.epoch_base.data_ptr()))
+
+    def stages(self, collective: str = "push") -> Iterator[None]:
+        """The block chain on this device's rows; every `yield` is a point where, on a single GPU standing in for
+        several, the other ranks' launches of the same step must be queued before this rank waits for them."""
+        with torch.cuda.stream(self.stream):
+            yield from self._stages(collective)
+
+    def _stages(self, collective: str) -> Iterator[None]:
+        from . import ops
+        d, st, t = self.dims, self.stream, self.tokens
+        first, count = self.rows
+        h, inter, qkvg, kvw = d.hidden, d.inter, d.qkvg, self.kv_width
+        q_heads = h // d.head_dim
+        x, attn = self.x[:count], self.attn_gu.view(-1)[: count * h].view(count, h)
+        gu = self.attn_gu.view(-1)[: count * inter].view(count, inter)
+        self.epoch = 0
+        for i, w in enumerate(self.blocks):
+            m, b = self.mods[i], i % 2
+            ops.prepare_norm_i8(x, w["prenorm"], m[0], m[1], self.a_q, self.a_s, h, self.ph, 1e-5, st)
+            ops.gemm_i8_256(count, self.a_q, w["qkvg.q"], w["qkvg.s"], self.a_s, self.fused, h, self.ph, qkvg, stream=st)
+            if collective == "push":
+                ops.rope_qknorm_f16_sharded(count, self.fused, w["qnorm"], w["knorm"], self.cos, self.sin, self.q, qkvg,
+                                            q_heads, d.kv_heads, h, self._shard(b), stream=st)
+                yield
+                self._wait()
+            else:
+                import torch.distributed as dist
+                ops.rope_qknorm_f16(self.fused, w["qnorm"], w["knorm"], self.cos, self.sin, self.q, self.k_local,
+                                    self.v_local, qkvg, q_heads, d.kv_heads, h, stream=st, tokens=count)
+                rows = self.world * self.share
+                dist.all_gather_into_tensor(self.k[b][:rows], self.k_local, group=self.fabric.group)
+                dist.all_gather_into_tensor(self.v[b][:rows], self.v_local, group=self.fabric.group)
+            ops.v_transpose(self.v[b], self.vt, kvw, self.cap, st, rows=t)
+            ops.attention_gqa_rows(count, t, d.kv_heads, self.q, self.k[b], self.vt, attn, h, kvw, h, self.cap, self.SCALE, st)
+            ops.prepare_gated_i8(attn, self.fused.view(-1)[d.gate_offset:], self.a_q, self.a_s, h, self.ph, qkvg, st,
+                                 tokens=count)
+            ops.gemm_i8_resid_256(count, self.a_q, w["wo.q"], w["wo.s"], self.a_s, x, m[2], h, self.ph, h, stream=st)
+            ops.prepare_norm_i8(x, w["postnorm"], m[3], m[4], self.a_q, self.a_s, h, self.ph, 1e-5, st)
+            ops.gemm_i8_swiglu_256(count, self.a_q, w["gu.q"], w["gu.s"], self.a_s, gu, h, self.ph, 2 * inter, stream=st)
+            ops.prepare_plain_i8(gu, self.a_q, self.a_s, inter, self.pi, st)
+            ops.gemm_i8_resid_256x256(count, self.a_q, w["down.q"], w["down.s"], self.a_s, x, m[5], inter, self.pi, h,
+                                      schedule_rows=shape.gemm_schedule_rows(count), stream=st)
+        if collective == "push":
+            ops.shard_signal(self._shard(None), st)  # no peer still reads K or V once every device has signalled
+            yield
+            self._wait()
+            check(lib().krea2_shard_advance(st.cuda_stream, self.epoch_base.data_ptr(), self.epoch))
+
+    def load(self, x: torch.Tensor, mods: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+        """Copies this device's rows of x (device bf16 [tokens][hidden]) and of the HOST or device RoPE tables, and
+        the modulation tables, into the fixed buffers."""
+        first, count = self.rows
+        with torch.cuda.stream(self.stream):
+            self.x[:count].copy_(x[first:first + count], non_blocking=True)
+            self.mods.copy_(mods, non_blocking=True)
+            self.cos.copy_(cos.view(self.tokens, -1)[first:first + count], non_blocking=True)
+            self.sin.copy_(sin.view(self.tokens, -1)[first:first + count], non_blocking=True)
+
+    def forward(self, x: torch.Tensor, mods: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, collective: str = "push",
+                graph: bool = False, check: bool = False) -> torch.Tensor:
+        """Returns this device's rows of the new residual stream (`self.rows`).  With `graph` the chain is replayed
+        from a CUDA graph recorded on first use (one per `collective`); every rank must then call it the same
+        number of times, since the flags count forwards."""
+        self.load(x, mods, cos, sin)
+        if graph:
+            if collective not in self.graphs:
+                capture = torch.cuda.Stream()
+                capture.wait_stream(self.stream)
+                saved, self.stream = self.stream, capture
+                recorded = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(recorded, stream=capture):
+                    for _ in self.stages(collective):
+                        pass
+                self.stream = saved
+                self.graphs[collective] = recorded
+            with torch.cuda.stream(self.stream):
+                self.graphs[collective].replay()
+        else:
+            for _ in self.stages(collective):
+                pass
+        if check:
+            require_clean_status()
+        return self.x[: self.rows[1]]
+
+
+def run_emulated_rows(ranks: Sequence[TokenParallel], x, mods, cos, sin) -> List[torch.Tensor]:
+    """Drives every rank of a token-sharded `LocalFabric` run on one GPU, step by step."""
+    for r in ranks:
+        r.load(x, mods, cos, sin)
+    generators = [r.stages("push") for r in ranks]
+    while True:
+        finished = 0
+        for g in generators:
+            try:
+                next(g)
+            except StopIteration:
+                finished += 1
+        if finished == len(generators):
+            break
+    return [r.x[: r.rows[1]] for r in ranks]
 
 
 def run_emulated(ranks: Sequence[TensorParallel], x: torch.Tensor, mods: torch.Tensor) -> List[torch.Tensor]:

@@ -61,6 +61,11 @@ def threads() -> int:
     return int(lib().oracle_threads())
 
 
+def set_threads(n: int) -> None:
+    """OpenMP threads for later calls, overriding an inherited OMP_NUM_THREADS."""
+    lib().oracle_set_threads(int(n))
+
+
 # ------------------------------------------------------------------ conversions
 def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)

@@ -395,6 +395,17 @@ void oracle_transport_f16_to_bf16(const uint16_t *src, uint16_t *dst, size_t n) 
     for (size_t i = 0; i < n; i++) dst[i] = f32_to_bf16(f16_to_f32(src[i]));
 }
 
+/* Sets the number of OpenMP threads later calls use, whatever OMP_NUM_THREADS said at load time
+ * (a launcher such as torchrun exports OMP_NUM_THREADS=1 to its ranks). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -161,6 +161,40 @@ def test_profiled_forward_reports_the_reference_stage_labels(small):
     s.close()
 
 
+def test_profile_json_appends_the_raw_intervals_of_each_profiled_forward(small, tmp_path, monkeypatch):
+    """KREA2_PROFILE_JSON (src/session/mod.rs:438-459): one JSON line per profiled forward with tokens, layers
+    and the device interval of every launch; an unwritable path is an invalid-argument error naming the variable."""
+    import json
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, 64, 2)
+    x, mods, cos, sin = so.make_inputs(dims, 64, 2, seed=8)
+    path = tmp_path / "profile.jsonl"
+    monkeypatch.setenv("KREA2_PROFILE_JSON", str(path))
+    s.set_profile(True)
+    for _ in range(2):
+        s.run(stream, torch.from_numpy(x.copy()).view(torch.bfloat16), torch.from_numpy(mods), torch.from_numpy(cos),
+              torch.from_numpy(sin))
+    records = [json.loads(line) for line in path.read_text().splitlines()]
+    assert len(records) == 2
+    for record in records:
+        assert record["tokens"] == 64 and record["layers"] == 2
+        intervals = record["profile"]["intervals"]
+        assert len(intervals) == 2 * 11 and record["profile"]["frequency_hz"] == 1000000000
+        assert [i["label"] for i in intervals[:3]] == ["prepare", "gemm qkvg", "qk norm + rope"]
+        assert [i["block"] for i in intervals] == [0] * 11 + [1] * 11
+        assert all(i["end_tick"] >= i["start_tick"] for i in intervals)
+        assert all(b["start_tick"] >= a["start_tick"] for a, b in zip(intervals, intervals[1:]))
+        total_ms = sum(i["end_tick"] - i["start_tick"] for i in intervals) / 1e6
+        assert abs(total_ms - sum(ms for _, ms in s.stage_profile())) < 0.05 or record is records[0]
+    monkeypatch.setenv("KREA2_PROFILE_JSON", str(tmp_path / "missing" / "profile.jsonl"))
+    with pytest.raises(k.InvalidArgument, match="KREA2_PROFILE_JSON"):
+        s.run(stream, torch.from_numpy(x.copy()).view(torch.bfloat16), torch.from_numpy(mods), torch.from_numpy(cos),
+              torch.from_numpy(sin))
+    s.close()
+
+
 @pytest.mark.parametrize("tokens", [64, 300])
 def test_full_block_session_equals_the_oracle_chain_around_the_attention_kernel(small, tokens):
     """With attention on, a block is the reference's eleven launches.  Everything but attention is

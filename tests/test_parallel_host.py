@@ -26,6 +26,57 @@ def test_shard_columns_split_whole_tiles():
         assert first % 32 == 0 and count % 32 == 0
 
 
+def test_shard_rows_gives_equal_shares_and_a_short_last_one():
+    assert parallel.shard_rows(4608, 8) == [(576 * r, 576) for r in range(8)]
+    assert parallel.shard_rows(16896, 4)[3] == (12672, 4224)
+    assert parallel.shard_rows(300, 4) == [(0, 75), (75, 75), (150, 75), (225, 75)]
+    assert parallel.shard_rows(4115, 8)[7] == (3605, 510)  # 515 rows each, the last one shorter
+    assert sum(count for _, count in parallel.shard_rows(4115, 8)) == 4115
+    assert parallel.shard_rows(16, 1) == [(0, 16)]
+    with pytest.raises(k.InvalidArgument, match="do not give each"):
+        parallel.shard_rows(17, 8)  # shares of 3 rows leave the last two devices without one
+    with pytest.raises(k.InvalidArgument, match="world must be"):
+        parallel.shard_rows(64, 0)
+
+
+def _row_gather_worker(rank, world, port, failures):
+    """The token-sharded chain's NCCL baseline on gloo: equal padded shares all-gathered into the rows of the
+    full K tensor; rows past the sequence land beyond `tokens` and are never read."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        tokens, width = 37, 256
+        gen = torch.Generator().manual_seed(9)
+        want = torch.randn((tokens, width), generator=gen)
+        first, count = parallel.shard_rows(tokens, world)[rank]
+        share = -(-tokens // world)
+        local = torch.zeros((share, width))
+        local[:count] = want[first:first + count]
+        full = torch.full((world * share + 3, width), 7.0)
+        dist.all_gather_into_tensor(full[: world * share], local)
+        if not torch.equal(full[:tokens], want):
+            failures.put(f"rank {rank}: gathered rows differ")
+        if not torch.equal(full[world * share:], torch.full((3, width), 7.0)):
+            failures.put(f"rank {rank}: rows past the gathered range were written")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_gather_row_shares():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    procs = [ctx.Process(target=_row_gather_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert failures.empty(), failures.get()
+
+
 def _gather_worker(rank, world, port, failures):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
