@@ -289,6 +289,11 @@ def one_image_on_all_ranks(torch, dist, k, args, mdims, weights, rank, world, ba
     from krea2_hrx_b200 import parallel
     stream = torch.cuda.current_stream()
     tokens, layers = single.tokens(), single.layers()
+    if world > 1:  # ONE image: every rank works on rank 0's inputs
+        x_dev, mods_dev, cos, sin = x_dev.clone(), mods_dev.clone(), cos.cuda(), sin.cuda()
+        for t in (x_dev, mods_dev, cos, sin):
+            dist.broadcast(t, src=0)
+        cos, sin = cos.cpu(), sin.cpu()
     fabric = parallel.SymmetricFabric()
     out = {}
     iters = max(3, min(args.steps, 10))

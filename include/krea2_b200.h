@@ -97,6 +97,21 @@ int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const void *a, const
                              const float *a_scale, void *c, size_t k_size, size_t k_stride, size_t n_size,
                              size_t m_group);
 
+/* The hand-off between the gate|up GEMM and the down projection's prologue, fused (the reference launches
+ * gemm_i8_swiglu_256 then prepare_plain_i8, src/session/mod.rs:803-826; it has no fused form).
+ * krea2_gemm_i8_swiglu_rotated_256 is krea2_gemm_i8_swiglu_256 whose epilogue also applies the first three of
+ * prepare_plain_i8's four rotation stages (strides 1, 4, 16; each with its quarter and f16 rounding,
+ * kernels/prepare_plain_i8.loom:112-232) to the 64 consecutive outputs a thread owns, under the next tile's main
+ * loop; c then holds the f16 row after three stages.  krea2_prepare_rotated_i8 takes such a row through the last
+ * stage (stride 64, :259-278), the row maximum and the codes (:294-313).  Together they write exactly the q and
+ * q_scale that krea2_gemm_i8_swiglu_256 followed by krea2_prepare_plain_i8 writes.  n_size must be a multiple
+ * of 256. */
+int krea2_gemm_i8_swiglu_rotated_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                                     const float *a_scale, void *c, size_t k_size, size_t k_stride, size_t n_size,
+                                     size_t m_group);
+int krea2_prepare_rotated_i8(krea2_stream stream, size_t tokens, const void *h, void *q, float *q_scale, size_t width,
+                             size_t out_stride);
+
 /* The raw i32 accumulators acc [m][n_size] of the same contraction, for parity checks
  * (the reference's tests recompute them on the CPU, tests/quantized.rs:203-211). */
 int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
@@ -414,6 +429,12 @@ int krea2_session_buffer(const krea2_session *session, const char *name, void **
  * the gated prologue reads the query columns of the q|k|v|gate output in place of an attention
  * output, which keeps every remaining stage reproducible bit for bit on a CPU.  Returns the previous setting; a recorded graph is dropped. */
 int krea2_session_set_attention(krea2_session *session, int enable);
+
+/* Chooses how the SwiGLU output reaches the down projection's prologue: 0 = the reference's two launches
+ * (gemm_i8_swiglu_256, prepare_plain_i8), 1 = the fused pair (krea2_gemm_i8_swiglu_rotated_256,
+ * krea2_prepare_rotated_i8).  The results are the same bits.  A new session takes the build's default unless the
+ * environment sets KREA2_FUSED_ROTATION=0 or 1.  Returns the previous setting; a recorded graph is dropped. */
+int krea2_session_set_fused_rotation(krea2_session *session, int enable);
 
 /* Number of kernels of this library that one forward of `layers` blocks launches. */
 size_t krea2_session_launches_per_forward(const krea2_session *session);

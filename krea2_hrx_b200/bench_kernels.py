@@ -34,7 +34,8 @@ REFERENCE_M = [1043, 4095, 4096, 4109, 12301, 16397]  # benches/kernels.rs:64
 def gemm_case(kind, dims):
     h, qkv, inter = dims["hidden"], dims["qkv"], dims["inter"]
     return {"qkvg": ("gemm_i8_256", h, qkv), "wo": ("gemm_i8_resid_256", h, h), "gu": ("gemm_i8_swiglu_256", h, 2 * inter),
-            "down": ("gemm_i8_resid_256x256", inter, h), "acc": ("gemm_i8_acc", h, qkv)}[kind]
+            "down": ("gemm_i8_resid_256x256", inter, h), "acc": ("gemm_i8_acc", h, qkv),
+            "gurot": ("gemm_i8_swiglu_rotated_256", h, 2 * inter)}[kind]
 
 
 SUSTAIN_SECONDS = 0.0   # --sustain: also run every timed kernel back to back this long, sampling power and clock
@@ -125,6 +126,9 @@ def run_gemm(kind, m, dims, iters, warmup, flush):
     elif name == "gemm_i8_swiglu_256":
         c = torch.empty((m, n // 2), dtype=torch.float16, device="cuda")
         fn = lambda: ops.gemm_i8_swiglu_256(m, a, w, ws, a_scale, c, k, pitch, n)
+    elif name == "gemm_i8_swiglu_rotated_256":
+        c = torch.empty((m, n // 2), dtype=torch.float16, device="cuda")
+        fn = lambda: ops.gemm_i8_swiglu_rotated_256(m, a, w, ws, a_scale, c, k, pitch, n)
     elif name == "gemm_i8_resid_256":
         c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         fn = lambda: ops.gemm_i8_resid_256(m, a, w, ws, a_scale, c, gate, k, pitch, n)
@@ -164,6 +168,8 @@ def run_prologue(kind, m, dims, iters, warmup, flush):
     qs = torch.zeros(m, dtype=torch.float32, device="cuda")
     if kind == "norm":
         fn = lambda: ops.prepare_norm_i8(x, vec[0], vec[1], vec[2], q, qs, width, pitch, 1e-5)
+    elif kind == "rotated":
+        fn = lambda: ops.prepare_rotated_i8(x, q, qs, width, pitch)
     elif kind == "gated":
         offset = gate_stride - width
         view = gate.view(-1)[offset:]
@@ -266,10 +272,37 @@ def run_library(kind, m, dims, iters, warmup, flush):
     return out
 
 
+def run_energy(kind, m, dims, iters, warmup, flush):
+    """What limits the GEMM's sustained rate: the same q|k|v|gate launch back to back for 2.5 s with all-zero
+    operands (no bit toggles in the operand paths and multipliers), with uniform int8 codes and with
+    Gaussian-shaped codes, sampling board power and SM clock beside each.  Zero operands hold the full clock;
+    random ones sit at the power cap at a lower clock."""
+    h, n = dims["hidden"], dims["qkv"]
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    ws = torch.rand(n, generator=gen, device="cuda") * 1e-2
+    a_s = torch.rand(m, generator=gen, device="cuda") * 1e-2
+    c = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    fills = {
+        "zero": lambda shape_: torch.zeros(shape_, dtype=torch.int8, device="cuda"),
+        "uniform": lambda shape_: torch.randint(-127, 128, shape_, generator=gen, device="cuda", dtype=torch.int8),
+        "gaussian": lambda shape_: (torch.randn(shape_, generator=gen, device="cuda") * 30).clamp(-127, 127).to(torch.int8),
+    }
+    out = {"kernel": "gemm_i8_256 energy by operand values", "m": m, "n": n, "k": h}
+    for name, fill in fills.items():
+        a, w = fill((m, h)), fill((n, h))
+        fn = lambda: ops.gemm_i8_256(m, a, w, ws, a_s, c, h, h, n)
+        burst = burst_time(fn, iters, warmup, flush)
+        sustained = sustained_run(fn, 2.5)
+        gop = 2.0 * m * n * h / 1e9
+        out[name] = {"burst_tops": gop / burst, "sustained_tops": gop / sustained["sustained_ms"], **sustained}
+    return out
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--kernel", default="all",
-                        help="qkvg, wo, gu, down, acc, norm, gated, plain, rope, vt, attention, euler, guidance, modulation, calibration, gemms, prologues or all "
+                        help="qkvg, wo, gu, gurot, down, acc, norm, gated, plain, rotated, rope, vt, attention, euler, guidance, modulation, calibration, "
+                             "energy, gemms, prologues or all "
                              "(comma separated)")
     parser.add_argument("--m", default="4608", help="rows, comma separated; 'reference' = the reference's bench list")
     parser.add_argument("--dims", default="reference", choices=sorted(DIMS))
@@ -289,13 +322,14 @@ def main():
     dims = DIMS[args.dims]
     for kind in kinds:
         for m in rows:
-            runner = run_prologue if kind in ("norm", "gated", "plain") else \
+            runner = run_prologue if kind in ("norm", "gated", "plain", "rotated") else \
+                run_energy if kind == "energy" else \
                 run_attention if kind in ("rope", "vt", "attention") else \
                 run_sampler if kind in ("euler", "guidance", "modulation") else \
                 run_library if kind == "calibration" else run_gemm
             result = runner(kind, m, dims, args.iters, args.warmup, args.flush_l2)
             result["dims"] = args.dims
-            if SUSTAIN_SECONDS > 0 and kind != "calibration":
+            if SUSTAIN_SECONDS > 0 and kind not in ("calibration", "energy"):
                 result["sustained"] = dict(LAST_SUSTAINED)
             print(json.dumps(result), flush=True)
 

@@ -41,7 +41,7 @@ constexpr int kGemmThreads = (kEpilogueWarps + 2) * 32;
 constexpr int kStagingBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output on their way out
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after two seconds
 
-enum class Epi { Plain, Resid, Swiglu, Acc };
+enum class Epi { Plain, Resid, Swiglu, Acc, SwigluRot };
 
 enum StatusBits { kProducerTimedOut = 1, kMmaTimedOut = 2, kEpilogueTimedOut = 4, kDrainTimedOut = 8, kShardWaitTimedOut = 16 };
 
@@ -291,9 +291,61 @@ __device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
 // Output of one thread's 32 accumulator columns: 16-byte vectors per chunk and bytes per element.
 template <Epi E>
 struct Out {
-    static constexpr int kVectors = E == Epi::Acc ? 8 : (E == Epi::Swiglu ? 2 : 4);
+    static constexpr int kVectors = E == Epi::Acc ? 8 : ((E == Epi::Swiglu || E == Epi::SwigluRot) ? 2 : 4);
     static constexpr int kElementBytes = E == Epi::Acc ? 4 : 2;
 };
+
+// ---- the SwiGLU epilogue that also starts the next prologue's rotation (Epi::SwigluRot)
+// prepare_plain_i8 rotates every aligned group of 256 SwiGLU outputs with four radix-4 stages (strides 1, 4, 16,
+// 64), each followed by a quarter and an f16 rounding (kernels/prepare_plain_i8.loom:112-167, 213-232, 259-278).
+// An epilogue thread owns 64 consecutive outputs of one row, an aligned quarter of such a group, so the first
+// three stages touch nothing but its own registers and can run here, under the next tile's main loop; what
+// reaches memory is the f16 row after three stages, and the prologue that follows does the last stage, the
+// row maximum and the codes.  Same operations in the same order with the same roundings: the int8 codes and
+// scales equal those of the unfused pair bit for bit.
+struct Pair2 {
+    float a, b;
+};
+__device__ __forceinline__ Pair2 add2(Pair2 x, Pair2 y) { return Pair2{__fadd_rn(x.a, y.a), __fadd_rn(x.b, y.b)}; }
+__device__ __forceinline__ Pair2 sub2(Pair2 x, Pair2 y) { return Pair2{__fsub_rn(x.a, y.a), __fsub_rn(x.b, y.b)}; }
+// One radix-4 butterfly on both lanes of the pairs (kernels/prepare_plain_i8.loom:121-128).
+__device__ __forceinline__ void butterfly2(Pair2 &e0, Pair2 &e1, Pair2 &e2, Pair2 &e3) {
+    const Pair2 s01 = add2(e0, e1), s23 = add2(e2, e3), d01 = sub2(e0, e1), d23 = sub2(e2, e3);
+    e0 = add2(s01, d23);
+    e1 = sub2(s01, d23);
+    e2 = add2(d01, s23);
+    e3 = sub2(s23, d01);
+}
+// f32(h) * 0.25 for both halves of an f16x2 word.  The stage's quarter is applied to its inputs: a power of two
+// commutes with the f32 additions and with the f16 rounding that follows (nothing is near the f32 underflow).
+__device__ __forceinline__ Pair2 unpack_quarter(uint32_t w) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    return Pair2{__fmul_rn(f.x, 0.25f), __fmul_rn(f.y, 0.25f)};
+}
+__device__ __forceinline__ uint32_t pack_pair(Pair2 v) { return pack_half2(v.a, v.b); }
+// Strides 1 and 4 inside 16 consecutive f16-valued outputs o[0..15]; leaves them as eight f16x2 words in order.
+__device__ __forceinline__ void rotate16(const float (&o)[16], uint32_t *words) {
+    uint32_t w[8];
+#pragma unroll
+    for (int half = 0; half < 2; half++) {  // quads 2*half and 2*half + 1 ride in the two lanes of a pair
+        Pair2 e[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) e[i] = Pair2{__fmul_rn(o[8 * half + i], 0.25f), __fmul_rn(o[8 * half + 4 + i], 0.25f)};
+        butterfly2(e[0], e[1], e[2], e[3]);
+        w[4 * half + 0] = pack_half2(e[0].a, e[1].a);
+        w[4 * half + 1] = pack_half2(e[2].a, e[3].a);
+        w[4 * half + 2] = pack_half2(e[0].b, e[1].b);
+        w[4 * half + 3] = pack_half2(e[2].b, e[3].b);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {  // word i holds outputs 2i, 2i+1; its quad partners are words i+2, i+4, i+6
+        Pair2 e0 = unpack_quarter(w[i]), e1 = unpack_quarter(w[i + 2]), e2 = unpack_quarter(w[i + 4]), e3 = unpack_quarter(w[i + 6]);
+        butterfly2(e0, e1, e2, e3);
+        w[i] = pack_pair(e0), w[i + 2] = pack_pair(e1), w[i + 4] = pack_pair(e2), w[i + 6] = pack_pair(e3);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) words[i] = w[i];
+}
 
 // One thread's 32 consecutive accumulator columns of one row, starting at (shard-local) column n,
 // turned into that row's output vectors.  `prior` points at the same columns of the residual row.
@@ -338,7 +390,7 @@ __device__ __forceinline__ void epilogue_math(const int32_t (&acc)[32], const Ge
             }
             out[v] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-    } else if constexpr (E == Epi::Swiglu) {
+    } else if constexpr (E == Epi::Swiglu || E == Epi::SwigluRot) {
         // kernels/gemm_i8_swiglu_256.loom:612-660: columns n..n+15 are gate rows, n+16..n+31 the
         // matching up rows; 16 outputs at column n/2.
 #pragma unroll
@@ -383,10 +435,57 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs &g, uint32_t tmem_l
     const uint32_t row = row_base + lane;
     const bool in_range = row < g.m;
     // Output geometry in elements: row pitch, and the column of this launch's first output.
-    const size_t pitch = S ? g.c_pitch : (E == Epi::Swiglu ? g.n / 2 : g.n);
+    const size_t pitch = S ? g.c_pitch : ((E == Epi::Swiglu || E == Epi::SwigluRot) ? g.n / 2 : g.n);
     const size_t column0 = (S ? g.c_offset : 0);
     float as = 0.0f;
     if constexpr (E != Epi::Acc) as = in_range ? __ldg(g.a_scale + row) : 0.0f;
+    if constexpr (E == Epi::SwigluRot) {
+        static_assert(kChunks == 4 && P == 8 && !S, "a thread owns 128 accumulator columns = 64 outputs of its row");
+        uint32_t words[32];  // the thread's 64 outputs as f16x2 words, in order
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const uint32_t n = n0 + (first_chunk + cc) * 32;
+            int32_t acc[32];
+            tmem_load_32(tmem_lane_base + (first_chunk + cc) * 32, acc);
+            float o[16];
+            if (in_range) {
+                uint4 plain[2];
+                epilogue_math<E>(acc, g, n, as, nullptr, plain);  // the 16 f16 outputs of gemm_i8_swiglu_256
+                const uint32_t pw[8] = {plain[0].x, plain[0].y, plain[0].z, plain[0].w, plain[1].x, plain[1].y, plain[1].z, plain[1].w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pw[i]));
+                    o[2 * i] = f.x, o[2 * i + 1] = f.y;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) o[i] = 0.0f;
+            }
+            rotate16(o, words + 8 * cc);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {  // stride 16: word i of each 16-output block
+            Pair2 e0 = unpack_quarter(words[i]), e1 = unpack_quarter(words[8 + i]), e2 = unpack_quarter(words[16 + i]),
+                  e3 = unpack_quarter(words[24 + i]);
+            butterfly2(e0, e1, e2, e3);
+            words[i] = pack_pair(e0), words[8 + i] = pack_pair(e1), words[16 + i] = pack_pair(e2), words[24 + i] = pack_pair(e3);
+        }
+#pragma unroll
+        for (int v = 0; v < 8; v++)
+            *reinterpret_cast<uint4 *>(stage + lane * 128 + ((v ^ (lane & 7)) * 16)) =
+                make_uint4(words[4 * v], words[4 * v + 1], words[4 * v + 2], words[4 * v + 3]);
+        __syncwarp();
+        const size_t out_column = (n0 + first_chunk * 32) / 2;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int r = j * 4 + lane / 8, piece = lane % 8;
+            const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((piece ^ (r & 7)) * 16));
+            const uint32_t out_row = row_base + r;
+            if (out_row < g.m) store_out<false>(g, (out_row * pitch + out_column) * 2 + piece * 16, value);
+        }
+        __syncwarp();
+        return;
+    }
     int slot = 0;
     uint32_t flush_n = n0 + first_chunk * 32;  // accumulator column of the first piece awaiting a flush
 #pragma unroll 1
@@ -1021,7 +1120,7 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     CUtensorMap map_a, map_w;
     if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
     if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, (wide && !pair) ? 256 : 128)) return status;
-    if constexpr (E != Epi::Acc) {
+    if constexpr (E != Epi::Acc && E != Epi::SwigluRot) {
         if (shard) {
             if (pair) return launch_pair<E, true>(stream, map_a, map_w, args);
             return wide ? launch_instance<E, 256, true>(stream, map_a, map_w, args)
@@ -1029,8 +1128,13 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
         }
     }
     if (pair) return launch_pair<E>(stream, map_a, map_w, args);
-    return wide ? launch_instance<E, 256>(stream, map_a, map_w, args)
-                : launch_instance<E, 128>(stream, map_a, map_w, args);
+    if constexpr (E == Epi::SwigluRot) {
+        KREA2_REQUIRE(wide, "%s: n_size %zu must be a multiple of 256", name, n_size);
+        return launch_instance<E, 256>(stream, map_a, map_w, args);
+    } else {
+        return wide ? launch_instance<E, 256>(stream, map_a, map_w, args)
+                    : launch_instance<E, 128>(stream, map_a, map_w, args);
+    }
 }
 
 }  // namespace
@@ -1046,12 +1150,14 @@ int prepare_gemm_device() {
     if (int s = ensure_instance<Epi::Resid, 256>()) return s;
     if (int s = ensure_instance<Epi::Swiglu, 128>()) return s;
     if (int s = ensure_instance<Epi::Swiglu, 256>()) return s;
+    if (int s = ensure_instance<Epi::SwigluRot, 256>()) return s;
     if (int s = ensure_instance<Epi::Acc, 128>()) return s;
     if (int s = ensure_instance<Epi::Acc, 256>()) return s;
     int clusters = 0;
     if (int s = ensure_pair_instance<Epi::Plain>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::Resid>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::Swiglu>(&clusters)) return s;
+    if (int s = ensure_pair_instance<Epi::SwigluRot>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::Acc>(&clusters)) return s;
     return KREA2_OK;
 }
@@ -1097,6 +1203,15 @@ extern "C" int krea2_gemm_i8_swiglu_256(krea2_stream stream, size_t m, const voi
     if (int status = check_gemm("gemm_i8_swiglu_256", m, k_size, k_stride, n_size, m_group, 128, 128)) return status;
     return run_gemm<Epi::Swiglu>("gemm_i8_swiglu_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale, c,
                                  nullptr, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_swiglu_rotated_256(krea2_stream stream, size_t m, const void *a, const void *w,
+                                                const float *scale, const float *a_scale, void *c, size_t k_size,
+                                                size_t k_stride, size_t n_size, size_t m_group) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_swiglu_rotated_256", m, k_size, k_stride, n_size, m_group, 128, 256)) return status;
+    return run_gemm<Epi::SwigluRot>("gemm_i8_swiglu_rotated_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale,
+                                    c, nullptr, k_size, k_stride, n_size);
 }
 
 extern "C" int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,

@@ -626,7 +626,10 @@ struct PlainPlan {
     static constexpr int kBytes = kStageBytes + G::kWorkers * 2 * kSlotFloats * 4;
 };
 
-template <int CPL>
+// kRotated: the row arrives with the first three stages (strides 1, 4, 16) already applied by the SwiGLU
+// epilogue that wrote it (krea2_gemm_i8_swiglu_rotated_256); only the last stage, the row maximum and the codes
+// are left.
+template <int CPL, bool kRotated>
 __global__ void __launch_bounds__(Geometry<CPL, kPlainThreads>::kBlockThreads, 1)
 prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, float *__restrict__ q_scale,
                      size_t out_stride, size_t tokens) {
@@ -665,23 +668,34 @@ prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, flo
             const uint4 ra = stage[(buffer * 4 + 2 * c1) * G::kBlockThreads + threadIdx.x];
             const uint4 rb = stage[(buffer * 4 + 2 * c1 + 1) * G::kBlockThreads + threadIdx.x];
             const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
-            F2 e[8];
+            if constexpr (kRotated) {
+                // element k of chunk a (index bit 6 clear) in the low half, of chunk b in the high half
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const F2 fa = unpack_quarter_f16x2(aw[k]), fb = unpack_quarter_f16x2(bw[k]);
-                e[2 * k] = F2{fa.a, fb.a};
-                e[2 * k + 1] = F2{fa.b, fb.b};
+                for (int k = 0; k < 4; k++) {
+                    x[c1][2 * k] = __byte_perm(aw[k], bw[k], 0x5410);
+                    x[c1][2 * k + 1] = __byte_perm(aw[k], bw[k], 0x7632);
+                }
+            } else {
+                F2 e[8];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const F2 fa = unpack_quarter_f16x2(aw[k]), fb = unpack_quarter_f16x2(bw[k]);
+                    e[2 * k] = F2{fa.a, fb.a};
+                    e[2 * k + 1] = F2{fa.b, fb.b};
+                }
+                butterfly2(e[0], e[1], e[2], e[3]);
+                butterfly2(e[4], e[5], e[6], e[7]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) x[c1][k] = pack_f16x2(e[k]);
+#pragma unroll
+                for (int c = 0; c < 4; c++) split_stage_f16(x[c1][c], x[c1][c + 4], 1);
             }
-            butterfly2(e[0], e[1], e[2], e[3]);
-            butterfly2(e[4], e[5], e[6], e[7]);
-#pragma unroll
-            for (int k = 0; k < 8; k++) x[c1][k] = pack_f16x2(e[k]);
-#pragma unroll
-            for (int c = 0; c < 4; c++) split_stage_f16(x[c1][c], x[c1][c + 4], 1);
         }
         if (row + G::kWorkers < rows.end) fetch(row + G::kWorkers, buffer ^ 1);
+        if constexpr (!kRotated) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) split_stage_f16(x[0][e], x[1][e], 2);
+            for (int e = 0; e < 8; e++) split_stage_f16(x[0][e], x[1][e], 2);
+        }
 #pragma unroll
         for (int c1 = 0; c1 < 2; c1++)
 #pragma unroll
@@ -827,21 +841,25 @@ struct LaunchGated {
     }
 };
 
-template <int CPL>
-struct LaunchPlain {
+template <int CPL, bool kRotated>
+struct LaunchPlainAs {
     static int run(cudaStream_t stream, size_t tokens, const void *h, void *q, float *q_scale,
                    size_t out_stride) {
         using G = Geometry<CPL, kPlainThreads>;
         static std::atomic<bool> done[kMaxDevices];
         int device = 0;
         if (int s = current_device(&device)) return s;
-        if (int s = allow_shared(prepare_plain_kernel<CPL>, PlainPlan<CPL>::kBytes, done, device)) return s;
-        prepare_plain_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
-                                    PlainPlan<CPL>::kBytes, stream>>>(
+        if (int s = allow_shared(prepare_plain_kernel<CPL, kRotated>, PlainPlan<CPL>::kBytes, done, device)) return s;
+        prepare_plain_kernel<CPL, kRotated><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
+                                              PlainPlan<CPL>::kBytes, stream>>>(
             static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride, tokens);
-        return finish_launch("prepare_plain_i8");
+        return finish_launch(kRotated ? "prepare_rotated_i8" : "prepare_plain_i8");
     }
 };
+template <int CPL>
+using LaunchPlain = LaunchPlainAs<CPL, false>;
+template <int CPL>
+using LaunchRotated = LaunchPlainAs<CPL, true>;
 
 // The `config.decl` ranges of the three kernels (kernels/prepare_norm_i8.loom:11-16,
 // prepare_gated_i8.loom:11-16, prepare_plain_i8.loom:10-13) and the reference's launch
@@ -955,6 +973,15 @@ extern "C" int krea2_prepare_plain_i8(krea2_stream stream, size_t tokens, const 
     KREA2_REQUIRE(h && q && q_scale, "prepare_plain_i8: null buffer");
     KREA2_REQUIRE(aligned16(h) && aligned16(q), "prepare_plain_i8: buffers must be 16-byte aligned");
     return dispatch_width<LaunchPlain>(width, static_cast<cudaStream_t>(stream), tokens, h, q, q_scale, out_stride);
+}
+
+extern "C" int krea2_prepare_rotated_i8(krea2_stream stream, size_t tokens, const void *h, void *q, float *q_scale,
+                                        size_t width, size_t out_stride) {
+    clear_error();
+    if (int status = check_prologue("prepare_rotated_i8", tokens, width, out_stride)) return status;
+    KREA2_REQUIRE(h && q && q_scale, "prepare_rotated_i8: null buffer");
+    KREA2_REQUIRE(aligned16(h) && aligned16(q), "prepare_rotated_i8: buffers must be 16-byte aligned");
+    return dispatch_width<LaunchRotated>(width, static_cast<cudaStream_t>(stream), tokens, h, q, q_scale, out_stride);
 }
 
 extern "C" int krea2_lora_transport(krea2_stream stream, size_t elements, const void *src, void *dst, int reverse) {

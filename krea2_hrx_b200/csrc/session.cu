@@ -153,6 +153,7 @@ struct krea2_session {
     cudaGraphExec_t graph = nullptr;
     bool profile = false, poisoned = false;
     bool attention = true;  // false: the W8A8 chain alone, the query columns in the attention output's place
+    bool fused_rotation = false;  // the gate|up epilogue starts the down projection's rotation (same bits either way)
     bool rope_valid = false;
     uint64_t rope_print[2] = {0, 0};
     std::vector<Stage> stages;
@@ -214,6 +215,9 @@ int block_pointers(const krea2_session *s, size_t index, BlockPointers *b) {
 // At most eleven launches per block (src/session/mod.rs:671-840); a profiled forward brackets
 // each with an event and sums device time per label.
 constexpr int kMaxStagesPerBlock = 11;
+// Whether a new session hands the SwiGLU output to the down projection's prologue through the fused pair
+// (krea2_gemm_i8_swiglu_rotated_256 + krea2_prepare_rotated_i8); KREA2_FUSED_ROTATION=0/1 overrides it.
+constexpr bool kFusedRotationDefault = false;
 
 // One block's launches in the reference's order.  `events`, when given, receives one event before
 // every stage and one after the last; `labels`, when given, the stage labels in launch order.
@@ -265,9 +269,16 @@ int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *
                                                              mods + 2 * hidden, hidden, ph, hidden, group))
     KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.postnorm, mods + 3 * hidden, mods + 4 * hidden, s->a_q,
                                                 s->a_s, hidden, ph, 1e-5f))
-    KREA2_STEP("gemm gate|up + swiglu", krea2_gemm_i8_swiglu_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu, hidden,
-                                                                 ph, 2 * inter, group))
-    KREA2_STEP("prepare swiglu", krea2_prepare_plain_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
+    if (s->fused_rotation) {
+        // The same two stages with three of the prologue's four rotation stages moved into the GEMM's epilogue.
+        KREA2_STEP("gemm gate|up + swiglu", krea2_gemm_i8_swiglu_rotated_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s,
+                                                                             s->attn_gu, hidden, ph, 2 * inter, group))
+        KREA2_STEP("prepare swiglu", krea2_prepare_rotated_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
+    } else {
+        KREA2_STEP("gemm gate|up + swiglu", krea2_gemm_i8_swiglu_256(stream, t, s->a_q, w.gu_q, w.gu_s, s->a_s, s->attn_gu,
+                                                                     hidden, ph, 2 * inter, group))
+        KREA2_STEP("prepare swiglu", krea2_prepare_plain_i8(stream, t, s->attn_gu, s->a_q, s->a_s, inter, pi))
+    }
     KREA2_STEP("gemm down + residual",
                krea2_gemm_i8_resid_256x256(stream, t, s->a_q, w.down_q, w.down_s, s->a_s, s->x, mods + 5 * hidden, inter, pi,
                                            hidden, group, static_cast<size_t>(krea2_shape_gemm_schedule_rows(t))))
@@ -540,6 +551,8 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     p->weights = weights;
     const char *env = getenv("KREA2_NATIVE_PROFILE");  // src/kernels/mod.rs:43-45
     p->profile = env && std::string(env) == "1";
+    const char *fused = getenv("KREA2_FUSED_ROTATION");
+    p->fused_rotation = fused ? std::string(fused) == "1" : kFusedRotationDefault;
     *out = guard.release();
     return KREA2_OK;
 }
@@ -576,6 +589,19 @@ extern "C" size_t krea2_session_stage_profile(const krea2_session *s, const char
 extern "C" size_t krea2_session_launches_per_forward(const krea2_session *s) {
     // eleven kernels per block with attention; eight without
     return s ? s->layers * (s->attention ? 11 : 8) : 0;
+}
+
+extern "C" int krea2_session_set_fused_rotation(krea2_session *s, int enable) {
+    if (!s) return 0;
+    const int previous = s->fused_rotation ? 1 : 0;
+    if ((enable != 0) != s->fused_rotation) {
+        s->fused_rotation = enable != 0;
+        if (s->graph) {  // the recording holds the other launch list
+            cudaGraphExecDestroy(s->graph);
+            s->graph = nullptr;
+        }
+    }
+    return previous;
 }
 
 extern "C" int krea2_session_set_attention(krea2_session *s, int enable) {

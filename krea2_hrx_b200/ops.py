@@ -101,6 +101,18 @@ def gemm_i8_swiglu_256(m, a, w, scale, a_scale, c, k_size, k_stride, n_size, m_g
                                          _ptr(c), k_size, k_stride, n_size, m_group))
 
 
+def gemm_i8_swiglu_rotated_256(m, a, w, scale, a_scale, c, k_size, k_stride, n_size, m_group=4, stream=None):
+    """gemm_i8_swiglu_256 whose epilogue also applies the first three rotation stages of prepare_plain_i8."""
+    check(lib().krea2_gemm_i8_swiglu_rotated_256(_stream_ptr(stream), m, _ptr(a), _ptr(w), _ptr(scale), _ptr(a_scale),
+                                                 _ptr(c), k_size, k_stride, n_size, m_group))
+
+
+def prepare_rotated_i8(h, q, q_scale, width, out_stride, stream=None):
+    """The rest of prepare_plain_i8 (last stage, row maximum, codes) on a row gemm_i8_swiglu_rotated_256 wrote."""
+    check(lib().krea2_prepare_rotated_i8(_stream_ptr(stream), h.shape[0], _ptr(h), _ptr(q), _ptr(q_scale), width,
+                                         out_stride))
+
+
 def gemm_i8_acc(m, a, w, acc, k_size, k_stride, n_size, stream=None):
     check(lib().krea2_gemm_i8_acc(_stream_ptr(stream), m, _ptr(a), _ptr(w), _ptr(acc), k_size, k_stride, n_size))
 

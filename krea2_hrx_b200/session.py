@@ -140,6 +140,11 @@ class Session:
         """Full block (True) or the W8A8 chain alone, the query columns in the attention output's place (False)."""
         return bool(lib().krea2_session_set_attention(self._handle, int(enable)))
 
+    def set_fused_rotation(self, enable: bool) -> bool:
+        """The SwiGLU output's hand-off to the down projection: the reference's two launches (False) or the fused
+        pair whose GEMM epilogue starts the prologue's rotation (True); the same bits either way."""
+        return bool(lib().krea2_session_set_fused_rotation(self._handle, int(enable)))
+
     def stage_profile(self) -> List[Tuple[str, float]]:
         labels = (ctypes.c_char_p * 16)()
         millis = (ctypes.c_double * 16)()

@@ -138,9 +138,14 @@ def test_sharded_chain_on_two_gpus_fused_and_nccl():
     worker = os.path.join(os.path.dirname(__file__), "tp_worker.py")
     world = min(torch.cuda.device_count(), 4)
     world = 2 if world < 4 else 4
-    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-                             "--master-addr", "127.0.0.1", "--master-port", str(port), worker, "--check"],
-                            capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    try:
+        result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                                 "--master-addr", "127.0.0.1", "--master-port", str(port), worker, "--check"],
+                                capture_output=True, text=True, timeout=240, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    except subprocess.TimeoutExpired as late:
+        def text(b):
+            return (b.decode(errors="replace") if isinstance(b, bytes) else (b or ""))[-3000:]
+        pytest.fail("the sharded worker did not finish: " + text(late.stdout) + text(late.stderr))
     assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
     assert "tp check ok" in result.stdout
 

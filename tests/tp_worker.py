@@ -53,10 +53,21 @@ def main():
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         return bool(flag.item())
 
+    held = {}  # the sharded runners: dropped (with their recorded graphs) before the process group goes
+
+    def say(text: str):
+        if rank == 0:
+            print(text, flush=True)
+
     def leave(code: int):
+        import gc
         torch.cuda.synchronize()
         fabric.barrier()
+        held.clear()
+        gc.collect()
+        torch.cuda.empty_cache()
         single.close()
+        fabric.barrier()
         dist.destroy_process_group()
         sys.exit(code)
 
@@ -65,7 +76,7 @@ def main():
     want = x_dev.clone()
     single.run_device(stream, want, mods_dev, cos_t, sin_t)
     torch.cuda.synchronize()
-    tp = parallel.TensorParallel(fabric, rank, dims, parallel.shard_weights(weights, layers, world, rank), tokens)
+    tp = held["tp"] = parallel.TensorParallel(fabric, rank, dims, parallel.shard_weights(weights, layers, world, rank), tokens)
     fabric.barrier()
     for mode in ("fused", "nccl", "fused", "graph fused", "graph fused", "graph nccl", "graph nccl"):
         if mode.startswith("graph"):
@@ -74,15 +85,17 @@ def main():
             out = tp.forward(x_dev, mods_dev, mode)
         fabric.barrier()
         if not agreed(np.array_equal(bits(out), bits(want))):
-            if rank == 0:
-                print(f"column-sharded chain ({mode}): a rank's result differs", flush=True)
+            say(f"column-sharded chain ({mode}): a rank's result differs")
             leave(1)
+        say(f"column-sharded chain ({mode}): ok")
+    del tp
+    held.clear()
     # token-sharded rows: the full block, attention on
     single.set_attention(True)
     want = x_dev.clone()
     single.run_device(stream, want, mods_dev, cos_t, sin_t)
     torch.cuda.synchronize()
-    sp = parallel.TokenParallel(fabric, rank, weights, tokens, layers)
+    sp = held["sp"] = parallel.TokenParallel(fabric, rank, weights, tokens, layers)
     fabric.barrier()
     for mode in ("push", "nccl", "graph push", "graph push", "graph nccl"):
         graph, collective = mode.startswith("graph"), mode.split()[-1]
@@ -90,15 +103,14 @@ def main():
         fabric.barrier()
         first, count = sp.rows
         if not agreed(np.array_equal(bits(out), bits(want[first:first + count]))):
-            if rank == 0:
-                print(f"token-sharded chain ({mode}): a rank's rows differ", flush=True)
+            say(f"token-sharded chain ({mode}): a rank's rows differ")
             leave(1)
+        say(f"token-sharded chain ({mode}): ok")
+    del sp
     if not agreed(k.device_status() == 0):
-        if rank == 0:
-            print("a rank's device status was raised", flush=True)
+        say("a rank's device status was raised")
         leave(1)
-    if rank == 0:
-        print("tp check ok", flush=True)
+    say("tp check ok")
     leave(0)
 
 
