@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -189,6 +190,7 @@ constexpr int kAttnThreads = 352;     // warps 0-3 and 4-7: the two softmax grou
 constexpr int kGroupWarps = 4;
 constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9, kTmaWarpV = 10;
 constexpr int kKvStages = 2;
+constexpr int kExponentialsOnFma = 1;  // pairs of keys on the FMA pipes per pair on the exponential unit
 constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
 constexpr int kAttnSmemBytes = (2 + 2 * kKvStages) * kOperandBytes + 1024 + 1024;  // Q x2, K, V stages, barriers
 
@@ -314,6 +316,46 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two f32 values in one 64-bit register pair and the packed arithmetic on them (one issue slot for two lanes).
+struct F2 {
+    float a, b;
+};
+#define KREA2_ATTN_PACKED(name, op)                                                                            \
+    __device__ __forceinline__ F2 name(F2 x, F2 y) {                                                           \
+        F2 d;                                                                                                  \
+        asm("{ .reg .b64 p, q, r;\n mov.b64 p, {%2, %3};\n mov.b64 q, {%4, %5};\n " op                        \
+            ".rn.f32x2 r, p, q;\n mov.b64 {%0, %1}, r;\n }"                                                    \
+            : "=f"(d.a), "=f"(d.b)                                                                             \
+            : "f"(x.a), "f"(x.b), "f"(y.a), "f"(y.b));                                                         \
+        return d;                                                                                              \
+    }
+KREA2_ATTN_PACKED(add2, "add")
+KREA2_ATTN_PACKED(sub2, "sub")
+#undef KREA2_ATTN_PACKED
+__device__ __forceinline__ F2 fma2(F2 x, F2 y, F2 z) {
+    F2 d;
+    asm("{ .reg .b64 p, q, r, s;\n mov.b64 p, {%2, %3};\n mov.b64 q, {%4, %5};\n mov.b64 r, {%6, %7};\n"
+        " fma.rn.f32x2 s, p, q, r;\n mov.b64 {%0, %1}, s;\n }"
+        : "=f"(d.a), "=f"(d.b)
+        : "f"(x.a), "f"(x.b), "f"(y.a), "f"(y.b), "f"(z.a), "f"(z.b));
+    return d;
+}
+// 2^x for both lanes on the FMA pipes, for the share of the exponentials the exponential unit is spared:
+// x = n + r with n the nearest integer (the magic-constant addition leaves it in the low mantissa bits) and
+// |r| <= 1/2, 2^r by a cubic (relative error 7.5e-5, a fifth of an f16 ulp: the result is rounded to f16 next),
+// and n added into the exponent field.  x is clamped at -120 so that the exponent never wraps; such
+// probabilities round to zero in f16 either way.
+__device__ __forceinline__ F2 exp2_on_fma(F2 x) {
+    const F2 magic = {12582912.0f, 12582912.0f};  // 1.5 * 2^23
+    x.a = fmaxf(x.a, -120.0f), x.b = fmaxf(x.b, -120.0f);
+    const F2 t = add2(x, magic);
+    const F2 r = sub2(x, sub2(t, magic));
+    F2 p = fma2(F2{0.0551716685f, 0.0551716685f}, r, F2{0.2426111251f, 0.2426111251f});
+    p = fma2(p, r, F2{0.6932609677f, 0.6932609677f});
+    p = fma2(p, r, F2{0.9999280572f, 0.9999280572f});
+    return F2{__uint_as_float(__float_as_uint(p.a) + (__float_as_uint(t.a) << 23)),
+              __uint_as_float(__float_as_uint(p.b) + (__float_as_uint(t.b) << 23))};
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -462,19 +504,19 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const uint32_t s = j % kKvStages, phase = (j / kKvStages) & 1u;
                 const uint32_t next = (j + 1) % kKvStages, next_phase = ((j + 1) / kKvStages) & 1u;
                 const bool more = j + 1 < tiles;
+                // The operands of this round (V of tile j, K of tile j + 1) were requested long ago: they are
+                // waited for first, so that nothing stands between a group's P arriving and its products.
+                alive = mbar_wait(v_full + s, phase, abort_flag) && (!more || mbar_wait(k_full + next, next_phase, abort_flag));
+                if (!alive) break;
 #pragma unroll
                 for (uint32_t grp = 0; grp < 2; grp++) {
                     // P V of this tile, then the group's next scores: the pipe keeps them in this order,
                     // so the scores overwrite P only after it has been read.
-                    alive = alive && mbar_wait(p_full + grp, j & 1u, abort_flag);
-                    if (grp == 0) alive = alive && mbar_wait(v_full + s, phase, abort_flag);
+                    alive = mbar_wait(p_full + grp, j & 1u, abort_flag);
                     if (!alive) break;
                     tc_fence_after();
                     issue_values(tmem_base + (2 + grp) * kTile, tmem_base + grp * kTile, smem_u32(v_smem + s * kOperandBytes), j > 0);
                     if (more) {
-                        if (grp == 0) alive = mbar_wait(k_full + next, next_phase, abort_flag);
-                        if (!alive) break;
-                        tc_fence_after();
                         issue_scores(tmem_base + grp * kTile, smem_u32(q_smem + grp * kOperandBytes),
                                      smem_u32(k_smem + next * kOperandBytes));
                         umma_commit(s_full + grp);
@@ -503,26 +545,39 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             tc_fence_after();
             const uint32_t valid = g.tokens - j * kTile;  // keys of this tile before the end of the sequence
-            // The whole row of S (128 scores) comes into registers with four loads in flight at once.
-            float v[kTile];
+            // Pass 1, the row maximum: the 128 scores pass through registers in two halves (they are read again
+            // for the exponentials, which keeps half as many registers live as holding the row would).
+            auto load_half = [&](int half, float (&v)[64]) {
+                tmem_load_32_async(s_addr + half * 64, v);
+                tmem_load_32_async(s_addr + half * 64 + 32, v + 32);
+                tmem_wait_load();
+                if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
 #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_load_32_async(s_addr + c * 32, v + c * 32);
-            tmem_wait_load();
-            if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
+                    for (int i = 0; i < 64; i++)
+                        if (static_cast<uint32_t>(half * 64 + i) >= valid) v[i] = -INFINITY;
+                }
+            };
+            float part[8];  // eight running maxima, two new scores each per 3-input max
+            {
+                float v[64];
+                load_half(0, v);
 #pragma unroll
-                for (int i = 0; i < kTile; i++)
-                    if (static_cast<uint32_t>(i) >= valid) v[i] = -INFINITY;
+                for (int k = 0; k < 8; k++) part[k] = max3(v[k], v[k + 8], v[k + 16]);
+#pragma unroll
+                for (int i = 24; i < 56; i += 16)
+#pragma unroll
+                    for (int k = 0; k < 8; k++) part[k] = max3(part[k], v[i + k], v[i + 8 + k]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) part[k] = fmaxf(part[k], v[56 + k]);
             }
-            // Eight running maxima, two new scores each per 3-input max.
-            float part[8];
+            {
+                float v[64];
+                load_half(1, v);
 #pragma unroll
-            for (int i = 0; i < 8; i++) part[i] = max3(v[i], v[i + 8], v[i + 16]);
+                for (int i = 0; i < 64; i += 16)
 #pragma unroll
-            for (int i = 24; i < kTile - 8; i += 16)
-#pragma unroll
-                for (int k = 0; k < 8; k++) part[k] = max3(part[k], v[i + k], v[i + 8 + k]);
-#pragma unroll
-            for (int k = 0; k < 8; k++) part[k] = fmaxf(part[k], v[kTile - 8 + k]);
+                    for (int k = 0; k < 8; k++) part[k] = max3(part[k], v[i + k], v[i + 8 + k]);
+            }
             float tile_max = fmaxf(max3(part[0], part[1], part[2]), max3(max3(part[3], part[4], part[5]), part[6], part[7]));
             tile_max *= g.scale_log2;
             // The exponent reference moves only when the maximum has grown by more than 2^8.
@@ -546,21 +601,34 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             // p = 2^(score - reference) as f16 pairs, back into the first 64 columns of the S region:
             // key 2c in the low half of column c, which is the A operand layout of the P V product.
-            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // The exponential unit does 16 lanes a clock per SM, which makes 128 x 128 exponentials the longest
+            // part of this phase: of every 1 + kExponentialsOnFma pairs of keys one goes to the unit and the
+            // others take the FMA pipes, in packed arithmetic (exp2_on_fma).
+            const F2 scale2 = {g.scale_log2, g.scale_log2}, shift2 = {-reference, -reference};
+            F2 partial[4] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};
 #pragma unroll
             for (int c = 0; c < 2; c++) {
+                // keys 64 c .. 64 c + 63 become words 32 c .. of P; the columns a store overwrites have been read
+                float v[64];
+                load_half(c, v);
                 uint32_t packed[32];
 #pragma unroll
                 for (int i = 0; i < 64; i += 2) {
-                    const float p0 = fast_exp2(fmaf(v[c * 64 + i], g.scale_log2, -reference));
-                    const float p1 = fast_exp2(fmaf(v[c * 64 + i + 1], g.scale_log2, -reference));
-                    partial[(i >> 1) & 3] += p0 + p1;
-                    const __half2 h = __floats2half2_rn(p0, p1);
+                    const F2 x = fma2(F2{v[i], v[i + 1]}, scale2, shift2);
+                    F2 pr;
+                    if ((i >> 1) % (1 + kExponentialsOnFma) == 0) {
+                        pr = F2{fast_exp2(x.a), fast_exp2(x.b)};
+                    } else {
+                        pr = exp2_on_fma(x);  // a masked key's -inf is clamped there and rounds to zero in f16
+                    }
+                    partial[(i >> 1) & 3] = add2(partial[(i >> 1) & 3], pr);
+                    const __half2 h = __floats2half2_rn(pr.a, pr.b);
                     packed[i / 2] = *reinterpret_cast<const uint32_t *>(&h);
                 }
                 tmem_store_32_async(s_addr + c * 32, packed);
             }
-            sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
+            const F2 total = add2(add2(partial[0], partial[1]), add2(partial[2], partial[3]));
+            sum += total.a + total.b;
             tmem_wait_store();
             tc_fence_before();
             __syncwarp();
