@@ -10,7 +10,8 @@ import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_size_t, c_uint16, c_uint32, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libkrea2_b200.so")
+# KREA2_B200_LIB names another build of the same library (e.g. one compiled with other build-time choices).
+LIB_PATH = os.environ.get("KREA2_B200_LIB") or os.path.join(HERE, "libkrea2_b200.so")
 
 
 class Error(RuntimeError):

@@ -190,7 +190,21 @@ constexpr int kAttnThreads = 352;     // warps 0-3 and 4-7: the two softmax grou
 constexpr int kGroupWarps = 4;
 constexpr int kTmaWarpAttn = 8, kMmaWarpAttn = 9, kTmaWarpV = 10;
 constexpr int kKvStages = 2;
-constexpr int kExponentialsOnFma = 1;  // pairs of keys on the FMA pipes per pair on the exponential unit
+// Build-time choices of the softmax phase (the defaults are what measured best inside the block loop):
+// KREA2_ATTN_TWO_PASS   1: the scores pass through registers in halves, once for the maximum and once for the
+//                          exponentials; 0: the whole row stays in registers
+// KREA2_ATTN_FMA_PAIRS  of every KREA2_ATTN_UNIT_PAIRS + KREA2_ATTN_FMA_PAIRS pairs of keys, how many take
+//                          their exponentials on the FMA pipes (exp2_on_fma) instead of the exponential unit
+#ifndef KREA2_ATTN_TWO_PASS
+#define KREA2_ATTN_TWO_PASS 1
+#endif
+#ifndef KREA2_ATTN_FMA_PAIRS
+#define KREA2_ATTN_FMA_PAIRS 1
+#endif
+#ifndef KREA2_ATTN_UNIT_PAIRS
+#define KREA2_ATTN_UNIT_PAIRS 3
+#endif
+constexpr int kUnitPairs = KREA2_ATTN_UNIT_PAIRS, kFmaPairs = KREA2_ATTN_FMA_PAIRS;  // of every kUnitPairs + kFmaPairs pairs of keys, how many go where
 constexpr uint64_t kAttnWaitLimitNs = 2000000000ull;
 constexpr int kAttnSmemBytes = (2 + 2 * kKvStages) * kOperandBytes + 1024 + 1024;  // Q x2, K, V stages, barriers
 
@@ -528,7 +542,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             if (alive) umma_commit(o_done);
         }
-    } else {
+    } else if (warp < 2 * kGroupWarps) {
         // Softmax group `grp` owns query rows q0 + 128 grp .. + 127: warp w reads TMEM lanes 32 (w % 4) .. + 31,
         // one row per thread.
         const int grp = warp >> 2, quarter = warp & 3;
@@ -545,19 +559,23 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             tc_fence_after();
             const uint32_t valid = g.tokens - j * kTile;  // keys of this tile before the end of the sequence
+            float part[8];  // eight running maxima, two new scores each per 3-input max
+            auto mask_tail = [&](int first, int count, float *v) {
+                if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
+#pragma unroll
+                    for (int i = 0; i < count; i++)
+                        if (static_cast<uint32_t>(first + i) >= valid) v[i] = -INFINITY;
+                }
+            };
+#if KREA2_ATTN_TWO_PASS
             // Pass 1, the row maximum: the 128 scores pass through registers in two halves (they are read again
             // for the exponentials, which keeps half as many registers live as holding the row would).
             auto load_half = [&](int half, float (&v)[64]) {
                 tmem_load_32_async(s_addr + half * 64, v);
                 tmem_load_32_async(s_addr + half * 64 + 32, v + 32);
                 tmem_wait_load();
-                if (valid < static_cast<uint32_t>(kTile)) {  // the last tile: keys past the sequence score -inf
-#pragma unroll
-                    for (int i = 0; i < 64; i++)
-                        if (static_cast<uint32_t>(half * 64 + i) >= valid) v[i] = -INFINITY;
-                }
+                mask_tail(half * 64, 64, v);
             };
-            float part[8];  // eight running maxima, two new scores each per 3-input max
             {
                 float v[64];
                 load_half(0, v);
@@ -578,6 +596,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                     for (int k = 0; k < 8; k++) part[k] = max3(part[k], v[i + k], v[i + 8 + k]);
             }
+#else
+            // The whole row of S (128 scores) comes into registers with four loads in flight at once.
+            float row[kTile];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_load_32_async(s_addr + c * 32, row + c * 32);
+            tmem_wait_load();
+            mask_tail(0, kTile, row);
+#pragma unroll
+            for (int i = 0; i < 8; i++) part[i] = max3(row[i], row[i + 8], row[i + 16]);
+#pragma unroll
+            for (int i = 24; i < kTile - 8; i += 16)
+#pragma unroll
+                for (int k = 0; k < 8; k++) part[k] = max3(part[k], row[i + k], row[i + 8 + k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) part[k] = fmaxf(part[k], row[kTile - 8 + k]);
+#endif
             float tile_max = fmaxf(max3(part[0], part[1], part[2]), max3(max3(part[3], part[4], part[5]), part[6], part[7]));
             tile_max *= g.scale_log2;
             // The exponent reference moves only when the maximum has grown by more than 2^8.
@@ -602,21 +636,48 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // p = 2^(score - reference) as f16 pairs, back into the first 64 columns of the S region:
             // key 2c in the low half of column c, which is the A operand layout of the P V product.
             // The exponential unit does 16 lanes a clock per SM, which makes 128 x 128 exponentials the longest
-            // part of this phase: of every 1 + kExponentialsOnFma pairs of keys one goes to the unit and the
-            // others take the FMA pipes, in packed arithmetic (exp2_on_fma).
+            // part of this phase: of every kUnitPairs + kFmaPairs pairs of keys the first kUnitPairs go to the
+            // unit and the others take the FMA pipes, in packed arithmetic (exp2_on_fma).
+#if KREA2_ATTN_FMA_PAIRS == 0
+            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+#if KREA2_ATTN_TWO_PASS
+                float v[64];
+                load_half(c, v);
+#else
+                const float *v = row + c * 64;
+#endif
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    const float p0 = fast_exp2(fmaf(v[i], g.scale_log2, -reference));
+                    const float p1 = fast_exp2(fmaf(v[i + 1], g.scale_log2, -reference));
+                    partial[(i >> 1) & 3] += p0 + p1;
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    packed[i / 2] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                tmem_store_32_async(s_addr + c * 32, packed);
+            }
+            sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
+#else
             const F2 scale2 = {g.scale_log2, g.scale_log2}, shift2 = {-reference, -reference};
             F2 partial[4] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};
 #pragma unroll
             for (int c = 0; c < 2; c++) {
                 // keys 64 c .. 64 c + 63 become words 32 c .. of P; the columns a store overwrites have been read
+#if KREA2_ATTN_TWO_PASS
                 float v[64];
                 load_half(c, v);
+#else
+                const float *v = row + c * 64;
+#endif
                 uint32_t packed[32];
 #pragma unroll
                 for (int i = 0; i < 64; i += 2) {
                     const F2 x = fma2(F2{v[i], v[i + 1]}, scale2, shift2);
                     F2 pr;
-                    if ((i >> 1) % (1 + kExponentialsOnFma) == 0) {
+                    if ((i >> 1) % (kUnitPairs + kFmaPairs) < kUnitPairs) {
                         pr = F2{fast_exp2(x.a), fast_exp2(x.b)};
                     } else {
                         pr = exp2_on_fma(x);  // a masked key's -inf is clamped there and rounds to zero in f16
@@ -629,6 +690,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             const F2 total = add2(add2(partial[0], partial[1]), add2(partial[2], partial[3]));
             sum += total.a + total.b;
+#endif
             tmem_wait_store();
             tc_fence_before();
             __syncwarp();

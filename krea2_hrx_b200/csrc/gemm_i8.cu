@@ -245,6 +245,7 @@ struct Tile {
 struct GemmArgs {
     uint32_t m, n, k_blocks;
     uint32_t n_group;      // pair kernel: output tile columns walked together (0: all rows of a column first)
+    uint32_t serpentine;   // pair kernel, grouped order: every other tile of a cluster walks K backwards
     const float *scale;    // [n] per output channel
     const float *a_scale;  // [m] per token
     const float *gate;     // [n], residual epilogue only
@@ -766,13 +767,18 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == kProducerWarp) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, local = 0;
             bool alive = true;
-            for (uint32_t tile = pair; alive && tile < tiles; tile += pairs) {
+            for (uint32_t tile = pair; alive && tile < tiles; tile += pairs, local++) {
                 uint32_t tile_m, tile_n;
                 tile_origin(tile, tile_m, tile_n);
                 const int m0 = static_cast<int>(tile_m * 2 * kBlockM + rank * kBlockM);
                 const int n0 = static_cast<int>(tile_n * BN + rank * (BN / 2));
+                // In the grouped order every other tile of a cluster walks K backwards.  All clusters are on
+                // the same local tile at about the same time, so a wave that ends at the high end of K is
+                // followed by one that starts there, on W panels whose high end is the part of them most
+                // recently in L2.  The accumulators are integer sums: the order of the K steps changes no bit.
+                const bool backwards = g.serpentine != 0 && (local & 1u) != 0;
                 for (uint32_t kb = 0; kb < g.k_blocks; kb++) {
                     if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, kProducerTimedOut)) {
                         alive = false;
@@ -781,8 +787,9 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t *a_dst = smem + stage * T::kStageBytes;
                     const uint32_t leader_full = map_to_cta(full + stage, 0);
                     if (leader) mbar_expect_tx(full + stage, 2 * T::kStageBytes);
-                    tma_load_2d_pair(a_dst, &map_a, leader_full, static_cast<int>(kb) * kBlockK, m0);
-                    tma_load_2d_pair(a_dst + T::kABytes, &map_w, leader_full, static_cast<int>(kb) * kBlockK, n0);
+                    const int k0 = static_cast<int>(backwards ? g.k_blocks - 1 - kb : kb) * kBlockK;
+                    tma_load_2d_pair(a_dst, &map_a, leader_full, k0, m0);
+                    tma_load_2d_pair(a_dst + T::kABytes, &map_w, leader_full, k0, n0);
                     issued++;
                     if (++stage == T::kStages) {
                         stage = 0;
@@ -1100,6 +1107,11 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.n = static_cast<uint32_t>(n_size);
     args.k_blocks = static_cast<uint32_t>((k_size + kBlockK - 1) / kBlockK);
     args.n_group = tile_column_group(m, k_size, n_size);
+    static const bool serpentine_enabled = [] {  // KREA2_GEMM_SERPENTINE=0 keeps every tile walking K forwards (for A/B runs)
+        const char *v = std::getenv("KREA2_GEMM_SERPENTINE");
+        return !(v && v[0] == '0');
+    }();
+    args.serpentine = (args.n_group != 0 && serpentine_enabled) ? 1u : 0u;
     args.scale = scale;
     args.a_scale = a_scale;
     args.gate = gate;
