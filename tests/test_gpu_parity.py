@@ -394,6 +394,44 @@ def test_config0_linear_tracks_the_reference_torch_scheme(ops):
         assert np.abs(out - ref).max() <= 2e-2 * np.abs(ref).max(), name
 
 
+@pytest.mark.parametrize("k_size", [2048, 4096])
+def test_config0_shape_class_through_prologue_and_gemm(ops, k_size):
+    """The single W8A8 linear of the benchmark's first configuration -- 256 tokens, 3072 outputs, f16 activations
+    ~N(0,1) with 1 % of the channels scaled by 20, int8 weights uniform in [-127,127], channel scales ~U(1e-3,1e-2)
+    -- at the two legal reduction widths on either side of its K = 3072 (the reference's prologues take widths
+    that are multiples of 2048, kernels/prepare_plain_i8.loom:10-13): prepare_plain_i8 then gemm_i8_256, every
+    code, scale, accumulator and output bit against the oracle."""
+    m, n = 256, 3072
+    rng = np.random.default_rng(k_size)
+    x = rng.standard_normal((m, k_size)).astype(np.float32)
+    x[:, rng.choice(k_size, size=k_size // 100, replace=False)] *= 20.0
+    x16 = kat.f16_bits(x)
+    w = rng.integers(-127, 128, size=(n, k_size), dtype=np.int16).astype(np.int8)
+    ws = rng.uniform(1e-3, 1e-2, size=n).astype(np.float32)
+    q = q_buffer(m, k_size)
+    qs = torch.zeros(m, dtype=torch.float32, device="cuda")
+    ops.prepare_plain_i8(dev(x16, torch.float16), q, qs, k_size, k_size)
+    want_q, want_s = oracle.prepare_plain_i8(x16, k_size, k_size, fill=0xA5)
+    np.testing.assert_array_equal(host(q, np.int8), want_q)
+    np.testing.assert_array_equal(host(qs, np.uint32), want_s.view(np.uint32))
+    acc = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    ops.gemm_i8_acc(m, q, dev(w), acc, k_size, k_size, n)
+    want_acc = oracle.gemm_i8_acc(want_q, w, k_size, k_size, n)
+    np.testing.assert_array_equal(host(acc, np.int32), want_acc)
+    c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    ops.gemm_i8_256(m, q, dev(w), dev(ws), qs, c, k_size, k_size, n)
+    np.testing.assert_array_equal(host(c, np.uint16), oracle.epilogue_plain(want_acc, ws, want_s))
+    # against the real-valued product the quantisation error stays at the W8A8 level
+    exact = x16_as_f64(x16) @ (w.astype(np.float64) * ws[:, None].astype(np.float64)).T
+    got = kat.f16_from_bits(host(c, np.uint16)).astype(np.float64)
+    finite = np.abs(exact) < 6e4
+    assert np.linalg.norm((got - exact)[finite]) / np.linalg.norm(exact[finite]) < 2e-2
+
+
+def x16_as_f64(bits16):
+    return kat.f16_from_bits(bits16).astype(np.float64)
+
+
 def test_unaligned_buffers_are_refused(ops):
     a = torch.zeros(128 * 128 + 16, dtype=torch.int8, device="cuda")
     w = torch.zeros((128, 128), dtype=torch.int8, device="cuda")
