@@ -464,6 +464,29 @@ def run_b200(args, dims, config):
     clocks = sampler.stop() if sampler else None
     launches_per_step = s.launches_per_forward() + 2  # the session's kernels, modulation and euler
 
+    # The same step back to back for three seconds with board power sampled beside it (rank 0): the step is bound
+    # by the 1 kW cap, so joules per step is the figure a kernel change has to move.  Not part of `value`.
+    sustained = None
+    if not args.no_sustained:
+        barrier()
+        power = ClockSampler(local) if rank == 0 else None
+        s_start, s_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count, began = 0, time.time()
+        s_start.record(stream)
+        while time.time() - began < 3.0:
+            for _ in range(4):
+                device_step()
+            count += 4
+            torch.cuda.synchronize()
+        s_end.record(stream)
+        barrier()
+        sustained_ms = s_start.elapsed_time(s_end) / count
+        if power:
+            sampled = power.stop(skip_first=0.34)
+            sustained = {"seconds": 3.0, "steps": count, "ms_per_step": sustained_ms, "sm_mhz": sampled["sm_mhz"],
+                         "watts": sampled["watts"], "reasons": sampled["reasons"],
+                         "joules_per_step": sampled["watts"] * sustained_ms * 1e-3 if sampled["watts"] else None}
+
     # The same 28 blocks without the three launches that are not W8A8 products.
     s.set_attention(False)
     chain_ms = timed_ms(torch, barrier, stream, lambda: s.run_device(stream, x_dev, mods_dev, cos, sin), args.steps)
@@ -613,6 +636,7 @@ def run_b200(args, dims, config):
                            "launches_per_step": layers * 8,
                            "what": "the same 28 blocks without QK-norm + RoPE, V transpose and attention (the query "
                                    "columns in the attention output's place)"},
+            "sustained": sustained,
             "device_status": status,
         }
         line.update(extra)
@@ -643,6 +667,7 @@ def main():
     parser.add_argument("--cpu-tokens", type=int, default=512, help="rows of the CPU baseline's bounded sample")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-calibration", action="store_true", help="skip the vendor-library int8 calibration")
+    parser.add_argument("--no-sustained", action="store_true", help="skip the three-second back-to-back run with power sampling")
     parser.add_argument("--no-sharded", action="store_true", help="N > 1: skip the one-image-on-all-ranks runs")
     parser.add_argument("--no-config4", action="store_true", help="N > 1: skip the 16896-token forward")
     parser.add_argument("--config4", action="store_true", help="N = 1: also run the 16896-token forward")

@@ -112,6 +112,21 @@ int krea2_gemm_i8_swiglu_rotated_256(krea2_stream stream, size_t m, const void *
 int krea2_prepare_rotated_i8(krea2_stream stream, size_t tokens, const void *h, void *q, float *q_scale, size_t width,
                              size_t out_stride);
 
+/* The q|k|v|gate product and the QK-norm + RoPE launch that follows it, fused (the reference launches gemm_i8_256
+ * then rope_qknorm_f16, src/session/mod.rs:702-734; it has no fused form).  The columns are heads of 128
+ * channels: q_heads query heads, kv_heads key heads, kv_heads value heads, then whatever is left (the attention
+ * gate).  An epilogue thread owns one row of one head, so the head's RMS norm (1 + scale, bf16), the rotation by
+ * the token's angles (bf16) and the f16 store happen on the values gemm_i8_256 would have written, in the
+ * standalone kernel's order of operations: q_out f16 [m][q_heads*128], k_out and v_out f16 [m][kv_heads*128]
+ * receive exactly what krea2_rope_qknorm_f16 writes from gemm_i8_256's output, and only the columns past the
+ * value heads are written to c (f16 [m][n_size]).  q_norm, k_norm f32 [128]; cos_table, sin_table f32 [m][128].
+ * n_size must be a multiple of 256. */
+int krea2_gemm_i8_rope_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                           const float *a_scale, void *c, const float *q_norm, const float *k_norm,
+                           const float *cos_table, const float *sin_table, void *q_out, void *k_out, void *v_out,
+                           size_t k_size, size_t k_stride, size_t n_size, size_t m_group, size_t q_heads,
+                           size_t kv_heads, float eps);
+
 /* The raw i32 accumulators acc [m][n_size] of the same contraction, for parity checks
  * (the reference's tests recompute them on the CPU, tests/quantized.rs:203-211). */
 int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,
@@ -435,6 +450,12 @@ int krea2_session_set_attention(krea2_session *session, int enable);
  * krea2_prepare_rotated_i8).  The results are the same bits.  A new session takes the build's default unless the
  * environment sets KREA2_FUSED_ROTATION=0 or 1.  Returns the previous setting; a recorded graph is dropped. */
 int krea2_session_set_fused_rotation(krea2_session *session, int enable);
+
+/* Chooses whether the q|k|v|gate GEMM also does the QK-norm + RoPE launch's work (krea2_gemm_i8_rope_256: ten
+ * launches per block instead of eleven; only with attention on).  The results are the same bits.  A new session
+ * takes the build's default unless the environment sets KREA2_FUSED_ROPE=0 or 1.  Returns the previous setting;
+ * a recorded graph is dropped. */
+int krea2_session_set_fused_rope(krea2_session *session, int enable);
 
 /* Number of kernels of this library that one forward of `layers` blocks launches. */
 size_t krea2_session_launches_per_forward(const krea2_session *session);

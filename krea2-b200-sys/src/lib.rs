@@ -124,6 +124,7 @@ extern "C" {
     pub fn krea2_gemm_i8_swiglu_256(stream: krea2_stream, m: usize, a: *const c_void, w: *const c_void, scale: *const f32, a_scale: *const f32, c: *mut c_void, k_size: usize, k_stride: usize, n_size: usize, m_group: usize) -> c_int;
     pub fn krea2_gemm_i8_swiglu_rotated_256(stream: krea2_stream, m: usize, a: *const c_void, w: *const c_void, scale: *const f32, a_scale: *const f32, c: *mut c_void, k_size: usize, k_stride: usize, n_size: usize, m_group: usize) -> c_int;
     pub fn krea2_prepare_rotated_i8(stream: krea2_stream, tokens: usize, h: *const c_void, q: *mut c_void, q_scale: *mut f32, width: usize, out_stride: usize) -> c_int;
+    pub fn krea2_gemm_i8_rope_256(stream: krea2_stream, m: usize, a: *const c_void, w: *const c_void, scale: *const f32, a_scale: *const f32, c: *mut c_void, q_norm: *const f32, k_norm: *const f32, cos_table: *const f32, sin_table: *const f32, q_out: *mut c_void, k_out: *mut c_void, v_out: *mut c_void, k_size: usize, k_stride: usize, n_size: usize, m_group: usize, q_heads: usize, kv_heads: usize, eps: f32) -> c_int;
     pub fn krea2_gemm_i8_acc(stream: krea2_stream, m: usize, a: *const c_void, w: *const c_void, acc: *mut i32, k_size: usize, k_stride: usize, n_size: usize) -> c_int;
     pub fn krea2_rope_qknorm_f16(stream: krea2_stream, tokens: usize, qkv: *const c_void, q_scale: *const f32, k_scale: *const f32, cos_table: *const f32, sin_table: *const f32, q_out: *mut c_void, k_out: *mut c_void, v_out: *mut c_void, row_stride: usize, q_heads: usize, kv_heads: usize, k_offset: usize, eps: f32) -> c_int;
     pub fn krea2_v_transpose(stream: krea2_stream, rows: usize, x: *const c_void, out: *mut c_void, width: usize, row_capacity: usize) -> c_int;
@@ -192,6 +193,7 @@ extern "C" {
     pub fn krea2_session_buffer(session: *const krea2_session, name: *const c_char, ptr: *mut *mut c_void, bytes: *mut usize) -> c_int;
     pub fn krea2_session_set_attention(session: *mut krea2_session, enable: c_int) -> c_int;
     pub fn krea2_session_set_fused_rotation(session: *mut krea2_session, enable: c_int) -> c_int;
+    pub fn krea2_session_set_fused_rope(session: *mut krea2_session, enable: c_int) -> c_int;
     pub fn krea2_session_launches_per_forward(session: *const krea2_session) -> usize;
 }
 

@@ -91,6 +91,9 @@ SIGNATURES = {
     "krea2_gemm_i8_swiglu_rotated_256": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                                  c_size_t, c_size_t, c_size_t]),
     "krea2_prepare_rotated_i8": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t]),
+    "krea2_gemm_i8_rope_256": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t,
+                                       c_size_t, c_size_t, c_float]),
     "krea2_gemm_i8_acc": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
     "krea2_rope_qknorm_f16": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_size_t, c_size_t, c_size_t, c_size_t, c_float]),
@@ -164,6 +167,7 @@ SIGNATURES = {
     "krea2_session_set_profile": (c_int, [c_void_p, c_int]),
     "krea2_session_set_attention": (c_int, [c_void_p, c_int]),
     "krea2_session_set_fused_rotation": (c_int, [c_void_p, c_int]),
+    "krea2_session_set_fused_rope": (c_int, [c_void_p, c_int]),
     "krea2_session_stage_profile": (c_size_t, [c_void_p, POINTER(c_char_p), POINTER(c_double), c_size_t]),
     "krea2_session_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t]),
     "krea2_session_run_device": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p,

@@ -35,7 +35,7 @@ def gemm_case(kind, dims):
     h, qkv, inter = dims["hidden"], dims["qkv"], dims["inter"]
     return {"qkvg": ("gemm_i8_256", h, qkv), "wo": ("gemm_i8_resid_256", h, h), "gu": ("gemm_i8_swiglu_256", h, 2 * inter),
             "down": ("gemm_i8_resid_256x256", inter, h), "acc": ("gemm_i8_acc", h, qkv),
-            "gurot": ("gemm_i8_swiglu_rotated_256", h, 2 * inter)}[kind]
+            "gurot": ("gemm_i8_swiglu_rotated_256", h, 2 * inter), "qkvgrope": ("gemm_i8_rope_256", h, qkv)}[kind]
 
 
 SUSTAIN_SECONDS = 0.0   # --sustain: also run every timed kernel back to back this long, sampling power and clock
@@ -123,6 +123,15 @@ def run_gemm(kind, m, dims, iters, warmup, flush):
     if name == "gemm_i8_256":
         c = torch.empty((m, n), dtype=torch.float16, device="cuda")
         fn = lambda: ops.gemm_i8_256(m, a, w, ws, a_scale, c, k, pitch, n)
+    elif name == "gemm_i8_rope_256":
+        q_heads, kv_heads = dims["hidden"] // 128, max(1, (n - 2 * dims["hidden"]) // 256)
+        c = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        q_out = torch.empty((m, q_heads * 128), dtype=torch.float16, device="cuda")
+        k_out, v_out = (torch.empty((m, kv_heads * 128), dtype=torch.float16, device="cuda") for _ in range(2))
+        norms = [torch.randn(128, generator=gen, device="cuda") * 0.1 for _ in range(2)]
+        cos, sin = torch.rand((m, 128), generator=gen, device="cuda"), torch.rand((m, 128), generator=gen, device="cuda")
+        fn = lambda: ops.gemm_i8_rope_256(m, a, w, ws, a_scale, c, norms[0], norms[1], cos, sin, q_out, k_out, v_out, k, pitch, n,
+                                          q_heads, kv_heads)
     elif name == "gemm_i8_swiglu_256":
         c = torch.empty((m, n // 2), dtype=torch.float16, device="cuda")
         fn = lambda: ops.gemm_i8_swiglu_256(m, a, w, ws, a_scale, c, k, pitch, n)

@@ -41,7 +41,7 @@ constexpr int kGemmThreads = (kEpilogueWarps + 2) * 32;
 constexpr int kStagingBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output on their way out
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every wait gives up after two seconds
 
-enum class Epi { Plain, Resid, Swiglu, Acc, SwigluRot };
+enum class Epi { Plain, Resid, Swiglu, Acc, SwigluRot, PlainRope };
 
 enum StatusBits { kProducerTimedOut = 1, kMmaTimedOut = 2, kEpilogueTimedOut = 4, kDrainTimedOut = 8, kShardWaitTimedOut = 16 };
 
@@ -260,6 +260,14 @@ struct GemmArgs {
     uint32_t *flags[8];
     uint32_t *done_counter;
     const uint32_t *epoch_base;  // optional device word added to `epoch` (lets a replayed graph count on)
+    // Epi::PlainRope: the q|k|v|gate product whose epilogue also does the QK-norm + RoPE launch's work.  Columns
+    // are heads of 128 channels: q_heads query heads, then kv_heads key heads, then kv_heads value heads, the
+    // rest (the attention gate) stays in `c`.
+    const float *rope_cos, *rope_sin;  // f32 [m][128]
+    const float *q_norm, *k_norm;      // f32 [128]
+    uint16_t *q_out, *k_out, *v_out;   // f16 [m][q_heads*128], [m][kv_heads*128], [m][kv_heads*128]
+    uint32_t q_heads, kv_heads;
+    float rope_eps;
 };
 
 // Stores one 16-byte vector at byte offset `at` of the output: into `c` alone, or into every
@@ -292,7 +300,7 @@ __device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
 // Output of one thread's 32 accumulator columns: 16-byte vectors per chunk and bytes per element.
 template <Epi E>
 struct Out {
-    static constexpr int kVectors = E == Epi::Acc ? 8 : ((E == Epi::Swiglu || E == Epi::SwigluRot) ? 2 : 4);
+    static constexpr int kVectors = E == Epi::Acc ? 8 : ((E == Epi::Swiglu || E == Epi::SwigluRot) ? 2 : 4);  // PlainRope as Plain
     static constexpr int kElementBytes = E == Epi::Acc ? 4 : 2;
 };
 
@@ -359,7 +367,7 @@ __device__ __forceinline__ void epilogue_math(const int32_t (&acc)[32], const Ge
         for (int i = 0; i < 8; i++)
             *reinterpret_cast<float4 *>(ws + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.scale + n) + i);
     }
-    if constexpr (E == Epi::Plain) {
+    if constexpr (E == Epi::Plain || E == Epi::PlainRope) {
 #pragma unroll
         for (int v = 0; v < 4; v++) {
             uint32_t w[4];
@@ -415,6 +423,119 @@ __device__ __forceinline__ void epilogue_math(const int32_t (&acc)[32], const Ge
     } else {
 #pragma unroll
         for (int v = 0; v < 8; v++) out[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+    }
+}
+
+// ---- the q|k|v|gate epilogue that also normalises and rotates q and k (Epi::PlainRope)
+// rope_qknorm_f16 (kernels/rope_qknorm_f16.loom:78-157) reads the f16 q and k heads this GEMM writes, normalises
+// each head of 128 channels (RMS with 1 + scale, bf16), rotates channel pairs by the token's angles (bf16) and
+// writes f16 q and k; v is copied.  An epilogue thread owns one row and 128 consecutive accumulator columns,
+// exactly one head, so all of it can happen here on the values the plain epilogue would have stored: the sum of
+// squares in the order the standalone kernel uses (four channels per partial, the 32 partials by the xor tree
+// 16, 8, 4, 2, 1), the same operations and roundings, hence the same bits.  The head's accumulators are read
+// from tensor memory twice, once for the sum and once for the outputs.
+__device__ __forceinline__ void dequant_chunk(const int32_t (&acc)[32], const GemmArgs &g, uint32_t n, float as, float (&x)[32]) {
+    float ws[32];
+#pragma unroll
+    for (int i = 0; i < 8; i++) *reinterpret_cast<float4 *>(ws + 4 * i) = __ldg(reinterpret_cast<const float4 *>(g.scale + n) + i);
+#pragma unroll
+    for (int i = 0; i < 32; i++) x[i] = __half2float(__float2half_rn(dequant(acc[i], ws[i], as)));  // what gemm_i8_256 stores
+}
+
+template <int kChunks>
+__device__ __forceinline__ void epilogue_tile_rope(const GemmArgs &g, uint32_t tmem_lane_base, uint32_t row_base, uint32_t n0,
+                                                   int first_chunk, uint8_t *stage, int lane) {
+    static_assert(kChunks == 4, "a thread owns 128 accumulator columns: one head");
+    const uint32_t row = row_base + lane;
+    const bool in_range = row < g.m;
+    const uint32_t column = n0 + first_chunk * 32, head = column / 128;  // the same for the whole warp
+    const bool is_q = head < g.q_heads, is_k = !is_q && head < g.q_heads + g.kv_heads;
+    const bool is_v = !is_q && !is_k && head < g.q_heads + 2 * g.kv_heads;
+    // Where this head's 128 columns go: element pointer of row 0 and the row pitch in elements.
+    uint16_t *dest;
+    size_t pitch;
+    if (is_q) dest = g.q_out + head * 128, pitch = static_cast<size_t>(g.q_heads) * 128;
+    else if (is_k) dest = g.k_out + (head - g.q_heads) * 128, pitch = static_cast<size_t>(g.kv_heads) * 128;
+    else if (is_v) dest = g.v_out + (head - g.q_heads - g.kv_heads) * 128, pitch = static_cast<size_t>(g.kv_heads) * 128;
+    else dest = static_cast<uint16_t *>(g.c) + column, pitch = g.n;
+    const float as = in_range ? __ldg(g.a_scale + row) : 0.0f;
+    float rinv = 0.0f;
+    if (is_q || is_k) {
+        float partial[32];  // partial[l]: the four channels 4l .. 4l + 3, as lane l of the standalone kernel sums them
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            int32_t acc[32];
+            tmem_load_32(tmem_lane_base + (first_chunk + cc) * 32, acc);
+            float x[32];
+            dequant_chunk(acc, g, column + cc * 32, as, x);
+#pragma unroll
+            for (int l = 0; l < 8; l++)
+                partial[8 * cc + l] = __fadd_rn(__fadd_rn(__fmul_rn(x[4 * l], x[4 * l]), __fmul_rn(x[4 * l + 1], x[4 * l + 1])),
+                                                __fadd_rn(__fmul_rn(x[4 * l + 2], x[4 * l + 2]), __fmul_rn(x[4 * l + 3], x[4 * l + 3])));
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+            for (int l = 0; l < off; l++) partial[l] = __fadd_rn(partial[l], partial[l + off]);
+        rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(partial[0], 0.0078125f), g.rope_eps)));
+    }
+    const float *norm = is_q ? g.q_norm : g.k_norm;
+    int slot = 0;
+#pragma unroll 1
+    for (int cc = 0; cc < 4; cc++) {
+        int32_t acc[32];
+        tmem_load_32(tmem_lane_base + (first_chunk + cc) * 32, acc);
+        uint4 out[4];
+        if (in_range) {
+            if (is_q || is_k) {
+                float x[32];
+                dequant_chunk(acc, g, column + cc * 32, as, x);
+                const float *cos_row = g.rope_cos + static_cast<size_t>(row) * 128 + cc * 32;
+                const float *sin_row = g.rope_sin + static_cast<size_t>(row) * 128 + cc * 32;
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {  // four channels at a time, as one lane of the standalone kernel
+                        const int c0 = 8 * v + 4 * h;
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(norm + cc * 32 + c0));
+                        const float4 cs = __ldg(reinterpret_cast<const float4 *>(cos_row + c0));
+                        const float4 sn = __ldg(reinterpret_cast<const float4 *>(sin_row + c0));
+                        const float x0 = bf_round(__fmul_rn(__fmul_rn(x[c0], rinv), __fadd_rn(sc.x, 1.0f)));
+                        const float x1 = bf_round(__fmul_rn(__fmul_rn(x[c0 + 1], rinv), __fadd_rn(sc.y, 1.0f)));
+                        const float x2 = bf_round(__fmul_rn(__fmul_rn(x[c0 + 2], rinv), __fadd_rn(sc.z, 1.0f)));
+                        const float x3 = bf_round(__fmul_rn(__fmul_rn(x[c0 + 3], rinv), __fadd_rn(sc.w, 1.0f)));
+                        const float o0 = bf_round(__fadd_rn(__fmul_rn(x0, cs.x), __fmul_rn(__fsub_rn(0.0f, x1), sn.x)));
+                        const float o1 = bf_round(__fadd_rn(__fmul_rn(x1, cs.y), __fmul_rn(x0, sn.y)));
+                        const float o2 = bf_round(__fadd_rn(__fmul_rn(x2, cs.z), __fmul_rn(__fsub_rn(0.0f, x3), sn.z)));
+                        const float o3 = bf_round(__fadd_rn(__fmul_rn(x3, cs.w), __fmul_rn(x2, sn.w)));
+                        w[2 * h] = pack_half2(o0, o1);
+                        w[2 * h + 1] = pack_half2(o2, o3);
+                    }
+                    out[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+                epilogue_math<Epi::PlainRope>(acc, g, column + cc * 32, as, nullptr, out);  // value and gate heads: as gemm_i8_256
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+            *reinterpret_cast<uint4 *>(stage + lane * 128 + (((slot + v) ^ (lane & 7)) * 16)) = out[v];
+        slot += 4;
+        if (slot == 8) {
+            __syncwarp();
+            const size_t out_column = static_cast<size_t>(cc - 1) * 32;  // the flush covers chunks cc - 1 and cc
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int r = j * 4 + lane / 8, piece = lane % 8;
+                const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((piece ^ (r & 7)) * 16));
+                const uint32_t out_row = row_base + r;
+                if (out_row < g.m)
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(dest + out_row * pitch + out_column) + piece * 16) = value;
+            }
+            __syncwarp();
+            slot = 0;
+        }
     }
 }
 
@@ -653,8 +774,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
             constexpr int kChunks = BN / 32 / kColumnGroups;
-            epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
-                                         lane);
+            if constexpr (E == Epi::PlainRope)
+                epilogue_tile_rope<kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes, lane);
+            else
+                epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
+                                             lane);
             tc_fence_before();
             mbar_arrive(acc_empty + a);
         }
@@ -843,8 +967,11 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const uint32_t lane_base = tmem_base + a * BN + (static_cast<uint32_t>(quarter * 32) << 16);
             constexpr int kChunks = BN / 32 / kColumnGroups;
-            epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
-                                         lane);
+            if constexpr (E == Epi::PlainRope)
+                epilogue_tile_rope<kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes, lane);
+            else
+                epilogue_tile<E, S, kChunks>(g, lane_base, m0 + quarter * 32, n0, group * kChunks, staging + warp * kStagingBytes,
+                                             lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty + a, 0));
@@ -1090,10 +1217,18 @@ uint32_t tile_column_group(size_t m, size_t k_size, size_t n_size) {
     return static_cast<uint32_t>(group < 1 ? 1 : (group >= panels ? 0 : group));
 }
 
+// What the PlainRope epilogue needs beyond the plain one's arguments.
+struct RopeArgs {
+    const float *cos, *sin, *q_norm, *k_norm;
+    void *q_out, *k_out, *v_out;
+    size_t q_heads, kv_heads;
+    float eps;
+};
+
 template <Epi E>
 int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, const void *w, const float *scale,
              const float *a_scale, void *c, const float *gate, size_t k_size, size_t k_stride, size_t n_size,
-             const krea2_shard *shard = nullptr) {
+             const krea2_shard *shard = nullptr, const RopeArgs *rope = nullptr) {
     KREA2_REQUIRE(a && w && c, "%s: null buffer", name);
     KREA2_REQUIRE(aligned16(a) && aligned16(w) && aligned16(c), "%s: buffers must be 16-byte aligned", name);
     if constexpr (E != Epi::Acc) {
@@ -1119,6 +1254,16 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     args.world = 1, args.rank = 0, args.c_pitch = 0, args.c_offset = 0, args.epoch = 0, args.done_counter = nullptr;
     args.epoch_base = nullptr;
     for (int d = 0; d < 8; d++) args.dest[d] = nullptr, args.flags[d] = nullptr;
+    args.rope_cos = args.rope_sin = args.q_norm = args.k_norm = nullptr;
+    args.q_out = args.k_out = args.v_out = nullptr;
+    args.q_heads = args.kv_heads = 0, args.rope_eps = 0.0f;
+    if constexpr (E == Epi::PlainRope) {
+        args.rope_cos = rope->cos, args.rope_sin = rope->sin, args.q_norm = rope->q_norm, args.k_norm = rope->k_norm;
+        args.q_out = static_cast<uint16_t *>(rope->q_out), args.k_out = static_cast<uint16_t *>(rope->k_out);
+        args.v_out = static_cast<uint16_t *>(rope->v_out);
+        args.q_heads = static_cast<uint32_t>(rope->q_heads), args.kv_heads = static_cast<uint32_t>(rope->kv_heads);
+        args.rope_eps = rope->eps;
+    }
     if (shard) {
         args.world = shard->world, args.rank = shard->rank, args.epoch = shard->epoch;
         args.c_pitch = static_cast<uint32_t>(shard->pitch), args.c_offset = static_cast<uint32_t>(shard->offset);
@@ -1132,7 +1277,7 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     CUtensorMap map_a, map_w;
     if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
     if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, (wide && !pair) ? 256 : 128)) return status;
-    if constexpr (E != Epi::Acc && E != Epi::SwigluRot) {
+    if constexpr (E != Epi::Acc && E != Epi::SwigluRot && E != Epi::PlainRope) {
         if (shard) {
             if (pair) return launch_pair<E, true>(stream, map_a, map_w, args);
             return wide ? launch_instance<E, 256, true>(stream, map_a, map_w, args)
@@ -1140,7 +1285,7 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
         }
     }
     if (pair) return launch_pair<E>(stream, map_a, map_w, args);
-    if constexpr (E == Epi::SwigluRot) {
+    if constexpr (E == Epi::SwigluRot || E == Epi::PlainRope) {
         KREA2_REQUIRE(wide, "%s: n_size %zu must be a multiple of 256", name, n_size);
         return launch_instance<E, 256>(stream, map_a, map_w, args);
     } else {
@@ -1163,6 +1308,7 @@ int prepare_gemm_device() {
     if (int s = ensure_instance<Epi::Swiglu, 128>()) return s;
     if (int s = ensure_instance<Epi::Swiglu, 256>()) return s;
     if (int s = ensure_instance<Epi::SwigluRot, 256>()) return s;
+    if (int s = ensure_instance<Epi::PlainRope, 256>()) return s;
     if (int s = ensure_instance<Epi::Acc, 128>()) return s;
     if (int s = ensure_instance<Epi::Acc, 256>()) return s;
     int clusters = 0;
@@ -1170,6 +1316,7 @@ int prepare_gemm_device() {
     if (int s = ensure_pair_instance<Epi::Resid>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::Swiglu>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::SwigluRot>(&clusters)) return s;
+    if (int s = ensure_pair_instance<Epi::PlainRope>(&clusters)) return s;
     if (int s = ensure_pair_instance<Epi::Acc>(&clusters)) return s;
     return KREA2_OK;
 }
@@ -1224,6 +1371,25 @@ extern "C" int krea2_gemm_i8_swiglu_rotated_256(krea2_stream stream, size_t m, c
     if (int status = check_gemm("gemm_i8_swiglu_rotated_256", m, k_size, k_stride, n_size, m_group, 128, 256)) return status;
     return run_gemm<Epi::SwigluRot>("gemm_i8_swiglu_rotated_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale,
                                     c, nullptr, k_size, k_stride, n_size);
+}
+
+extern "C" int krea2_gemm_i8_rope_256(krea2_stream stream, size_t m, const void *a, const void *w, const float *scale,
+                                      const float *a_scale, void *c, const float *q_norm, const float *k_norm,
+                                      const float *cos_table, const float *sin_table, void *q_out, void *k_out, void *v_out,
+                                      size_t k_size, size_t k_stride, size_t n_size, size_t m_group, size_t q_heads,
+                                      size_t kv_heads, float eps) {
+    clear_error();
+    if (int status = check_gemm("gemm_i8_rope_256", m, k_size, k_stride, n_size, m_group, 128, 256)) return status;
+    KREA2_REQUIRE(q_heads >= 1 && q_heads <= 256 && kv_heads >= 1 && kv_heads <= 256 && (q_heads + 2 * kv_heads) * 128 <= n_size,
+                  "gemm_i8_rope_256: %zu query and 2 x %zu key/value heads of 128 channels do not fit %zu columns", q_heads,
+                  kv_heads, n_size);
+    KREA2_REQUIRE(q_norm && k_norm && cos_table && sin_table && q_out && k_out && v_out, "gemm_i8_rope_256: null buffer");
+    KREA2_REQUIRE(aligned16(q_norm) && aligned16(k_norm) && aligned16(cos_table) && aligned16(sin_table) && aligned16(q_out) &&
+                      aligned16(k_out) && aligned16(v_out),
+                  "gemm_i8_rope_256: buffers must be 16-byte aligned");
+    const RopeArgs rope{cos_table, sin_table, q_norm, k_norm, q_out, k_out, v_out, q_heads, kv_heads, eps};
+    return run_gemm<Epi::PlainRope>("gemm_i8_rope_256", static_cast<cudaStream_t>(stream), m, a, w, scale, a_scale, c, nullptr,
+                                    k_size, k_stride, n_size, nullptr, &rope);
 }
 
 extern "C" int krea2_gemm_i8_acc(krea2_stream stream, size_t m, const void *a, const void *w, int32_t *acc,

@@ -154,6 +154,7 @@ struct krea2_session {
     bool profile = false, poisoned = false;
     bool attention = true;  // false: the W8A8 chain alone, the query columns in the attention output's place
     bool fused_rotation = false;  // the gate|up epilogue starts the down projection's rotation (same bits either way)
+    bool fused_rope = false;      // the q|k|v|gate epilogue does the QK-norm + RoPE launch's work (same bits either way)
     bool rope_valid = false;
     uint64_t rope_print[2] = {0, 0};
     std::vector<Stage> stages;
@@ -218,6 +219,9 @@ constexpr int kMaxStagesPerBlock = 11;
 // Whether a new session hands the SwiGLU output to the down projection's prologue through the fused pair
 // (krea2_gemm_i8_swiglu_rotated_256 + krea2_prepare_rotated_i8); KREA2_FUSED_ROTATION=0/1 overrides it.
 constexpr bool kFusedRotationDefault = false;
+// The same for the q|k|v|gate GEMM doing the QK-norm + RoPE launch's work (krea2_gemm_i8_rope_256);
+// KREA2_FUSED_ROPE=0/1 overrides it.
+constexpr bool kFusedRopeDefault = false;
 
 // One block's launches in the reference's order.  `events`, when given, receives one event before
 // every stage and one after the last; `labels`, when given, the stage labels in launch order.
@@ -244,13 +248,23 @@ int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *
     if ((status = (call))) return status;
     KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph,
                                                 1e-5f))
-    KREA2_STEP("gemm qkvg",
-               krea2_gemm_i8_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
+    const bool rope_in_gemm = s->attention && s->fused_rope;
+    if (rope_in_gemm) {
+        // The same two stages as one launch: q and k leave the GEMM's epilogue normalised and rotated.
+        KREA2_STEP("gemm qkvg", krea2_gemm_i8_rope_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, w.qnorm, w.knorm,
+                                                       s->cos, s->sin, s->q, s->k, s->v, hidden, ph, s->qkvg, group, q_heads,
+                                                       d.kv_heads, 1e-5f))
+    } else {
+        KREA2_STEP("gemm qkvg",
+                   krea2_gemm_i8_256(stream, t, s->a_q, w.qkvg_q, w.qkvg_s, s->a_s, s->fused, hidden, ph, s->qkvg, group))
+    }
     if (s->attention) {
         // src/session/mod.rs:714-755: QK norm + RoPE out of the fused buffer, V transposed, fp16 attention
-        KREA2_STEP("qk norm + rope",
-                   krea2_rope_qknorm_f16(stream, t, s->fused, w.qnorm, w.knorm, s->cos, s->sin, s->q, s->k, s->v, s->qkvg,
-                                         q_heads, d.kv_heads, hidden, 1e-5f))
+        if (!rope_in_gemm) {
+            KREA2_STEP("qk norm + rope",
+                       krea2_rope_qknorm_f16(stream, t, s->fused, w.qnorm, w.knorm, s->cos, s->sin, s->q, s->k, s->v, s->qkvg,
+                                             q_heads, d.kv_heads, hidden, 1e-5f))
+        }
         KREA2_STEP("V transpose", krea2_v_transpose(stream, t, s->v, s->v_transposed, kv_width, s->capacity))
         // shape::attention_source (src/kernels/shape.rs:24-31): the 32-query-row export from 8192 tokens on
         auto attention = krea2_shape_attention_rows(t) == 32 ? krea2_attention_gqa_lds_f16_wmma_q32
@@ -553,6 +567,8 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     p->profile = env && std::string(env) == "1";
     const char *fused = getenv("KREA2_FUSED_ROTATION");
     p->fused_rotation = fused ? std::string(fused) == "1" : kFusedRotationDefault;
+    const char *rope = getenv("KREA2_FUSED_ROPE");
+    p->fused_rope = (rope ? std::string(rope) == "1" : kFusedRopeDefault) && p->qkvg % 256 == 0;
     *out = guard.release();
     return KREA2_OK;
 }
@@ -587,8 +603,8 @@ extern "C" size_t krea2_session_stage_profile(const krea2_session *s, const char
     return n;
 }
 extern "C" size_t krea2_session_launches_per_forward(const krea2_session *s) {
-    // eleven kernels per block with attention; eight without
-    return s ? s->layers * (s->attention ? 11 : 8) : 0;
+    // eleven kernels per block with attention (ten when the q|k|v|gate GEMM also rotates); eight without
+    return s ? s->layers * (s->attention ? (s->fused_rope ? 10 : 11) : 8) : 0;
 }
 
 extern "C" int krea2_session_set_fused_rotation(krea2_session *s, int enable) {
@@ -596,6 +612,20 @@ extern "C" int krea2_session_set_fused_rotation(krea2_session *s, int enable) {
     const int previous = s->fused_rotation ? 1 : 0;
     if ((enable != 0) != s->fused_rotation) {
         s->fused_rotation = enable != 0;
+        if (s->graph) {  // the recording holds the other launch list
+            cudaGraphExecDestroy(s->graph);
+            s->graph = nullptr;
+        }
+    }
+    return previous;
+}
+
+extern "C" int krea2_session_set_fused_rope(krea2_session *s, int enable) {
+    if (!s) return 0;
+    const int previous = s->fused_rope ? 1 : 0;
+    const bool next = enable != 0 && s->qkvg % 256 == 0;
+    if (next != s->fused_rope) {
+        s->fused_rope = next;
         if (s->graph) {  // the recording holds the other launch list
             cudaGraphExecDestroy(s->graph);
             s->graph = nullptr;

@@ -113,6 +113,15 @@ def prepare_rotated_i8(h, q, q_scale, width, out_stride, stream=None):
                                          out_stride))
 
 
+def gemm_i8_rope_256(m, a, w, scale, a_scale, c, q_norm, k_norm, cos, sin, q_out, k_out, v_out, k_size, k_stride, n_size,
+                     q_heads, kv_heads, eps=1e-5, m_group=4, stream=None):
+    """gemm_i8_256 over q|k|v|gate columns whose epilogue also does rope_qknorm_f16's work: q, k normalised and
+    rotated, v copied, only the gate columns written to `c`."""
+    check(lib().krea2_gemm_i8_rope_256(_stream_ptr(stream), m, _ptr(a), _ptr(w), _ptr(scale), _ptr(a_scale), _ptr(c),
+                                       _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(q_out), _ptr(k_out), _ptr(v_out),
+                                       k_size, k_stride, n_size, m_group, q_heads, kv_heads, eps))
+
+
 def gemm_i8_acc(m, a, w, acc, k_size, k_stride, n_size, stream=None):
     check(lib().krea2_gemm_i8_acc(_stream_ptr(stream), m, _ptr(a), _ptr(w), _ptr(acc), k_size, k_stride, n_size))
 

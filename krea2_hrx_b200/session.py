@@ -145,6 +145,11 @@ class Session:
         pair whose GEMM epilogue starts the prologue's rotation (True); the same bits either way."""
         return bool(lib().krea2_session_set_fused_rotation(self._handle, int(enable)))
 
+    def set_fused_rope(self, enable: bool) -> bool:
+        """Whether the q|k|v|gate GEMM also does the QK-norm + RoPE launch's work (ten launches per block instead
+        of eleven, attention on only); the same bits either way."""
+        return bool(lib().krea2_session_set_fused_rope(self._handle, int(enable)))
+
     def stage_profile(self) -> List[Tuple[str, float]]:
         labels = (ctypes.c_char_p * 16)()
         millis = (ctypes.c_double * 16)()
