@@ -548,11 +548,20 @@ def run_b200(args, dims, config):
     s.set_profile(False)
     status = k.device_status()
 
+    # The legs after the headline: a failure that every rank meets alike (an allocation that does not fit, a
+    # library call this torch build lacks) is reported in the line instead of costing the numbers above.
     extra = {}
     if world > 1 and not args.no_sharded:
-        extra.update(one_image_on_all_ranks(torch, dist, k, args, mdims, weights, rank, world, barrier, s, x_dev, mods_dev, cos, sin))
+        try:
+            extra.update(one_image_on_all_ranks(torch, dist, k, args, mdims, weights, rank, world, barrier, s, x_dev, mods_dev,
+                                                cos, sin))
+        except Exception as error:  # noqa: BLE001
+            extra["sharded_runs_error"] = f"{type(error).__name__}: {error}"[:300]
     if (world > 1 or args.config4) and not args.no_config4:
-        extra["config4"] = largest_sequence(torch, k, session, args, mdims, weights, barrier, dist, world, rank)
+        try:
+            extra["config4"] = largest_sequence(torch, k, session, args, mdims, weights, barrier, dist, world, rank)
+        except Exception as error:  # noqa: BLE001
+            extra["config4"] = {"error": f"{type(error).__name__}: {error}"[:300]}
 
     if rank == 0:
         peaks, peak_source = measured_peaks()

@@ -26,7 +26,7 @@ from krea2_hrx_b200 import ops, shape  # noqa: E402
 DIMS = {
     # hidden, fused q|k|v|gate (or q|k|v) width, SwiGLU inner width
     "reference": dict(hidden=6144, qkv=15360, inter=16384),  # src/session/mod.rs:35-45
-    "baseline": dict(hidden=3072, qkv=9216, inter=8192),     # the dimensions BASELINE.json words
+    "baseline": dict(hidden=3072, qkv=9216, inter=8192),     # the benchmark brief's literal dimensions (d 3072, QKV 9216, SwiGLU 8192)
 }
 REFERENCE_M = [1043, 4095, 4096, 4109, 12301, 16397]  # benches/kernels.rs:64
 
