@@ -136,6 +136,35 @@ def test_a_session_refuses_a_foreign_stream_and_wrong_sizes(small):
     s.close()
 
 
+def test_run_device_refuses_tensors_of_the_wrong_kind(small):
+    """cos and sin are fingerprinted on the host and x and mods are read through raw device pointers, so a tensor on
+    the wrong side, of another dtype or non-contiguous must be refused before the library sees its address."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, 64, 2)
+    x, mods, cos, sin = so.make_inputs(dims, 64, 2, seed=12)
+    x_dev = torch.from_numpy(x.copy()).view(torch.bfloat16).cuda()
+    mods_dev, cos_t, sin_t = torch.from_numpy(mods).cuda(), torch.from_numpy(cos), torch.from_numpy(sin)
+    s.run_device(stream, x_dev, mods_dev, cos_t, sin_t)  # the well-formed call
+    with pytest.raises(k.InvalidArgument, match="cos/sin"):
+        s.run_device(stream, x_dev, mods_dev, cos_t.cuda(), sin_t)
+    with pytest.raises(k.InvalidArgument, match="cos/sin"):
+        s.run_device(stream, x_dev, mods_dev, cos_t.double(), sin_t.double())
+    with pytest.raises(k.InvalidArgument, match="cos/sin"):
+        s.run_device(stream, x_dev, mods_dev, cos_t.t().contiguous().t(), sin_t)
+    with pytest.raises(k.InvalidArgument, match="x as a contiguous CUDA bfloat16"):
+        s.run_device(stream, x_dev.cpu(), mods_dev, cos_t, sin_t)
+    with pytest.raises(k.InvalidArgument, match="x as a contiguous CUDA bfloat16"):
+        s.run_device(stream, x_dev.float(), mods_dev, cos_t, sin_t)
+    with pytest.raises(k.InvalidArgument, match="mods as a contiguous CUDA float32"):
+        s.run_device(stream, x_dev, mods_dev[:1].contiguous(), cos_t, sin_t)
+    with pytest.raises(k.InvalidArgument, match="mods as a contiguous CUDA float32"):
+        s.run_device(stream, x_dev, mods_dev.cpu(), cos_t, sin_t)
+    torch.cuda.synchronize()
+    s.close()
+
+
 def test_profiled_forward_reports_the_reference_stage_labels(small):
     """src/session/mod.rs:461-494, 627-647."""
     from krea2_hrx_b200 import session
