@@ -22,10 +22,11 @@ def bits(t):
     return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_sharded_chain_on_one_gpu_equals_the_session(world):
     from krea2_hrx_b200 import parallel, session
-    dims = session.ModelDims(**so.SMALL)
+    # eight shares of whole 128-column tiles need four key/value heads: q|k|v|gate = 5120 columns
+    dims = session.ModelDims(**(dict(so.SMALL, kv_heads=4) if world == 8 else so.SMALL))
     layers, tokens = 2, 300
     stream = torch.cuda.current_stream()
     weights = session.Weights(dims, layers)
@@ -50,7 +51,7 @@ def test_sharded_chain_on_one_gpu_equals_the_session(world):
     single.close()
 
 
-@pytest.mark.parametrize("world,tokens", [(1, 80), (2, 300), (4, 300), (3, 131)])
+@pytest.mark.parametrize("world,tokens", [(1, 80), (2, 300), (4, 300), (3, 131), (8, 300), (8, 1043)])
 def test_token_sharded_blocks_on_one_gpu_equal_the_session(world, tokens):
     """Rows of the sequence spread over `world` ranks that all live on this GPU: the full block, attention on,
     must give every rank exactly its rows of the single-device session's output."""
