@@ -348,8 +348,29 @@ def one_image_on_all_ranks(torch, dist, k, args, mdims, weights, rank, world, ba
                  "speedup": single_full_ms / push_ms, "speedup_nccl": single_full_ms / sp_nccl_ms,
                  "received_mb_per_gpu": kv_bytes * (world - 1) / world / 1e6,
                  "nvlink_floor_ms": kv_bytes * (world - 1) / world / 770e9 * 1e3}
+    # -- the 8-step loop of ONE image on the token-sharded ranks, against the same loop on one GPU
+    from krea2_hrx_b200 import pipeline
+    gen = torch.Generator().manual_seed(77)  # the same prompt, noise and tables on every rank
+    text_tokens = min(512, tokens // 2)
+    text = torch.randn((text_tokens, d.hidden), generator=gen).to(torch.bfloat16).cuda()
+    noise = torch.randn((tokens - text_tokens, d.hidden), generator=gen).to(torch.bfloat16).cuda()
+    tables = (torch.randn((layers, 6, d.hidden), generator=gen) * 0.1).to(torch.bfloat16).cuda()
+    vectors = [(torch.randn(6 * d.hidden, generator=gen) * 0.1).to(torch.bfloat16).cuda() for _ in range(8)]
+    alone = pipeline.Denoiser(single, tables, cos, sin, text, steps=8)
+    together = pipeline.ShardedDenoiser(sp, tables, cos, sin, text, steps=8, collective="push", graph=True)
+    want = alone.generate(noise.clone(), vectors)
+    got = together.gather(together.generate(noise.clone(), vectors))
+    fabric.barrier()
+    same = all_ranks_agree(torch, dist, world, torch.equal(got.view(torch.int16), want.view(torch.int16)))
+    alone_ms = timed_ms(torch, barrier, stream, lambda: alone.generate(noise.clone(), vectors), 2, warmup=1)
+    together_ms = timed_ms(torch, fabric.barrier, stream,
+                           lambda: together.gather(together.generate(noise.clone(), vectors)), 2, warmup=1)
+    alone_ms, together_ms = max_over_ranks(torch, dist, world, [alone_ms, together_ms])
+    out["sp"]["image"] = {"what": "8 Turbo steps of one image, rows sharded over the ranks from the first step to the "
+                                  "last, one gather of the sample at the end", "steps": 8, "bit_identical": same,
+                          "single_gpu_ms": alone_ms, "sharded_ms": together_ms, "speedup": alone_ms / together_ms}
     out["device_status_after_sharded_runs"] = k.device_status()
-    del sp
+    del sp, together
     torch.cuda.empty_cache()
     return out
 

@@ -474,6 +474,11 @@ class TokenParallel:
         from a CUDA graph recorded on first use (one per `collective`); every rank must then call it the same
         number of times, since the flags count forwards."""
         self.load(x, mods, cos, sin)
+        return self.replay(collective, graph, check)
+
+    def replay(self, collective: str = "push", graph: bool = False, check: bool = False) -> torch.Tensor:
+        """The chain on what the fixed buffers hold (`self.x[:count]`, `self.mods`, `self.cos`, `self.sin`): for a
+        caller that fills them itself, as the denoising loop does between steps."""
         if graph:
             if collective not in self.graphs:
                 capture = torch.cuda.Stream()

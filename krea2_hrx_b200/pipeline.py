@@ -100,3 +100,94 @@ class Denoiser:
                     raise Cancelled("generation cancelled")
             index += 1
         return sample
+
+
+class ShardedDenoiser:
+    """The same loop on one device's rows of a token-sharded image (`parallel.TokenParallel`).
+
+    Nothing between two steps crosses rows: the modulation tables are per block, and the Euler update of a
+    sample row needs that row's velocity only.  So a device keeps to its rows of `[text; image]` from the
+    first step to the last -- the keys and values inside each block are the only exchange -- and the caller
+    gathers `image_rows` of every device's sample once at the end.  Each device passes the whole sample
+    (bf16 `[image_tokens][hidden]`) and owns the rows `image_rows` of it; the others are left as they were.
+    Bit-identical to `Denoiser` on one device, row for row.  Guidance (a second forward per step) is not
+    offered here."""
+
+    def __init__(self, runner, tables: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, text: torch.Tensor,
+                 steps: int = 8, mu: Optional[float] = schedule.TURBO_MU, collective: str = "push", graph: bool = True):
+        dims, layers, tokens = runner.dims, runner.layers, runner.tokens
+        if not 1 <= steps <= 100:
+            raise InvalidArgument("invalid generation arguments")
+        if tables.dtype != torch.bfloat16 or tables.numel() != layers * 6 * dims.hidden or not tables.is_cuda:
+            raise InvalidArgument("tables must be device bf16 [layers][6][hidden]")
+        if text.dtype != torch.bfloat16 or text.dim() != 2 or text.shape[1] != dims.hidden or text.shape[0] >= tokens:
+            raise InvalidArgument("text must be device bf16 [text_tokens][hidden] with text_tokens < tokens")
+        self.runner, self.tables, self.steps = runner, tables.contiguous(), steps
+        self.collective, self.graph = collective, graph
+        self.text_tokens, self.image_tokens = text.shape[0], tokens - text.shape[0]
+        self.mu = schedule.dynamic_mu(self.image_tokens) if mu is None else mu
+        first, count = runner.rows
+        self.text_count = max(0, min(first + count, self.text_tokens) - first)
+        self.image_rows = (max(first, self.text_tokens) - self.text_tokens, count - self.text_count)
+        self.text_local = text[first:first + self.text_count].contiguous()
+        with torch.cuda.stream(runner.stream):
+            runner.cos.copy_(cos.view(tokens, -1)[first:first + count], non_blocking=True)
+            runner.sin.copy_(sin.view(tokens, -1)[first:first + count], non_blocking=True)
+        self._delta = 0.0
+
+    def _rows(self, sample: torch.Tensor) -> torch.Tensor:
+        if sample.dtype != torch.bfloat16 or tuple(sample.shape) != (self.image_tokens, self.runner.dims.hidden):
+            raise InvalidArgument("sample must be device bf16 [image_tokens][hidden]")
+        first, count = self.image_rows
+        return sample[first:first + count]
+
+    def begin_step(self, index: int, sample: torch.Tensor, vector: torch.Tensor, last: Optional[int] = None) -> float:
+        """What precedes the blocks: this step's modulation tables and this device's rows of `[text; image]`."""
+        last = self.steps if last is None else last
+        runner, mine = self.runner, self._rows(sample)
+        sigma = schedule.sigma(index, self.steps, self.mu)
+        self._delta = float(np.float32(schedule.next_sigma(index, last, self.steps, self.mu)) - np.float32(sigma))
+        with torch.cuda.stream(runner.stream):
+            ops.modulation(vector, self.tables, runner.mods, runner.stream)
+            count = runner.rows[1]
+            if self.text_count:
+                runner.x[: self.text_count].copy_(self.text_local, non_blocking=True)
+            if mine.shape[0]:
+                runner.x[self.text_count:count].copy_(mine, non_blocking=True)
+        return self._delta
+
+    def finish_step(self, sample: torch.Tensor) -> None:
+        """What follows the blocks: the Euler update of this device's sample rows from its velocity rows."""
+        runner, mine = self.runner, self._rows(sample)
+        if mine.shape[0]:
+            with torch.cuda.stream(runner.stream):
+                ops.euler_step(mine, runner.x[self.text_count:runner.rows[1]], self._delta, runner.stream)
+
+    def step(self, index: int, sample: torch.Tensor, vector: torch.Tensor, last: Optional[int] = None) -> float:
+        delta = self.begin_step(index, sample, vector, last)
+        self.runner.replay(self.collective, self.graph)
+        self.finish_step(sample)
+        return delta
+
+    def generate(self, sample: torch.Tensor, vectors: Sequence[torch.Tensor]) -> torch.Tensor:
+        """All steps on this device's rows of `sample` (updated in place; the other rows are not touched)."""
+        if len(vectors) < self.steps:
+            raise InvalidArgument("one modulation vector per step is needed")
+        for index in range(self.steps):
+            self.step(index, sample, vectors[index])
+        return sample
+
+    def gather(self, sample: torch.Tensor) -> torch.Tensor:
+        """Fills every device's `sample` with all devices' rows: one all-gather of the devices' equal, padded shares
+        of `[text; image]` over the runner's process group (`torch.distributed`)."""
+        import torch.distributed as dist
+        runner, mine = self.runner, self._rows(sample)
+        count = runner.rows[1]
+        with torch.cuda.stream(runner.stream):
+            local = torch.zeros((runner.share, sample.shape[1]), dtype=sample.dtype, device=sample.device)
+            if mine.shape[0]:
+                local[self.text_count:count].copy_(mine, non_blocking=True)
+            full = torch.empty((runner.world * runner.share, sample.shape[1]), dtype=sample.dtype, device=sample.device)
+            dist.all_gather_into_tensor(full, local, group=runner.fabric.group)
+            sample.copy_(full[self.text_tokens:runner.tokens], non_blocking=True)
+        return sample

@@ -131,3 +131,53 @@ def test_bad_arguments_are_refused():
     with pytest.raises(k.InvalidArgument):
         d.generate(dev16(case["sample"]), [dev16(case["vectors"][0])])  # one vector for two steps
     s.close()
+
+
+@pytest.mark.parametrize("world,text_tokens,image_tokens", [(2, 16, 120), (4, 40, 91), (3, 70, 61)])
+def test_the_token_sharded_loop_equals_the_loop_on_one_device(world, text_tokens, image_tokens):
+    """Every rank keeps to its rows of [text; image] through all steps (ranks emulated on this GPU, their launches
+    interleaved stage by stage); the rows each rank owns must equal the single-device loop's, full block with
+    attention.  The shares cut through the text/image boundary in different places: a rank of text rows only
+    (world 3), one of both, ranks of image rows only."""
+    from krea2_hrx_b200 import parallel
+    layers, steps = 3, 4
+    case = make_case(layers, text_tokens, image_tokens, steps, seed=20 + world)
+    s, d, _ = build(case, layers, steps, schedule.TURBO_MU, 0.0, attention=True)
+    vectors = [dev16(v) for v in case["vectors"]]
+    want = dev16(case["sample"])
+    d.generate(want, vectors)
+    fabric = parallel.LocalFabric(world)
+    runners = [parallel.TokenParallel(fabric, r, s.weights, case["tokens"], layers) for r in range(world)]
+    loops = [pipeline.ShardedDenoiser(run, dev16(case["tables"]), torch.from_numpy(case["cos"]), torch.from_numpy(case["sin"]),
+                                      dev16(case["text"]), steps=steps, graph=False) for run in runners]
+    assert sum(loop.image_rows[1] for loop in loops) == image_tokens
+    if world == 3:
+        assert loops[0].image_rows[1] == 0  # 44 rows of the 70 text tokens and nothing else
+    samples = [dev16(case["sample"]) for _ in range(world)]
+    for index in range(steps):
+        for loop, sample in zip(loops, samples):
+            loop.begin_step(index, sample, vectors[index])
+        generators = [run.stages("push") for run in runners]
+        while generators:
+            alive = []
+            for g in generators:
+                try:
+                    next(g)
+                    alive.append(g)
+                except StopIteration:
+                    pass
+            generators = alive
+        for loop, sample in zip(loops, samples):
+            loop.finish_step(sample)
+    got = dev16(case["sample"])  # rows no rank owns would stay as they started; every row has an owner
+    for loop, sample in zip(loops, samples):
+        first, count = loop.image_rows
+        got[first:first + count] = sample[first:first + count]
+        others = torch.ones(image_tokens, dtype=torch.bool)
+        others[first:first + count] = False
+        assert torch.equal(sample[others.cuda()].view(torch.int16), dev16(case["sample"])[others.cuda()].view(torch.int16))
+    np.testing.assert_array_equal(host16(got), host16(want))
+    assert k.device_status() == 0
+    with pytest.raises(k.InvalidArgument):
+        loops[0].begin_step(0, samples[0][:-1], vectors[0])
+    s.close()
