@@ -1217,6 +1217,24 @@ uint32_t tile_column_group(size_t m, size_t k_size, size_t n_size) {
     return static_cast<uint32_t>(group < 1 ? 1 : (group >= panels ? 0 : group));
 }
 
+// Whether 128-row tiles on single CTAs need clearly fewer rounds over the SMs than 256-row tiles on CTA pairs.
+// Both kinds of round do the same work (one 128 x 256 tile per SM), and the pair kernel's are the faster ones
+// (each CTA stages half of W); but when the row count leaves the last 256-row tile half empty -- an odd number
+// of 128-row halves, as with 1043 or 1152 rows -- the pairs can pay a whole extra round for it.  The single-CTA
+// kernel is taken when it saves at least one round in thirteen.  Integer sums: the choice changes no bit.
+bool fewer_rounds_in_halves(size_t m, size_t n_size) {
+    static const bool enabled = [] {  // KREA2_GEMM_HALVES=0 keeps the pair kernel (for A/B runs)
+        const char *v = std::getenv("KREA2_GEMM_HALVES");
+        return !(v && v[0] == '0');
+    }();
+    if (!enabled) return false;
+    const size_t sms = static_cast<size_t>(sm_count()), columns = n_size / 256;
+    if (sms < 2) return false;
+    const size_t pair_rounds = ((m + 255) / 256 * columns + sms / 2 - 1) / (sms / 2);
+    const size_t half_rounds = ((m + 127) / 128 * columns + sms - 1) / sms;
+    return half_rounds * 13 <= pair_rounds * 12;
+}
+
 // What the PlainRope epilogue needs beyond the plain one's arguments.
 struct RopeArgs {
     const float *cos, *sin, *q_norm, *k_norm;
@@ -1273,7 +1291,7 @@ int run_gemm(const char *name, cudaStream_t stream, size_t m, const void *a, con
     }
     const bool wide = n_size % 256 == 0;
     // The two-CTA kernel wants whole 256-column tiles and more than one 128-row half to fill.
-    const bool pair = wide && m > kBlockM && pair_enabled();
+    const bool pair = wide && m > kBlockM && pair_enabled() && !fewer_rounds_in_halves(m, n_size);
     CUtensorMap map_a, map_w;
     if (int status = make_operand_map(&map_a, a, m, k_size, k_stride, kBlockM)) return status;
     if (int status = make_operand_map(&map_w, w, n_size, k_size, k_stride, (wide && !pair) ? 256 : 128)) return status;
