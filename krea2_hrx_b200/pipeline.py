@@ -102,6 +102,12 @@ class Denoiser:
         return sample
 
 
+def share_of_image(first: int, count: int, text_tokens: int):
+    """Rows [first, first + count) of `[text; image]` as (text rows held, first image row, image rows held)."""
+    text_count = max(0, min(first + count, text_tokens) - first)
+    return text_count, max(first, text_tokens) - text_tokens, count - text_count
+
+
 class ShardedDenoiser:
     """The same loop on one device's rows of a token-sharded image (`parallel.TokenParallel`).
 
@@ -127,8 +133,8 @@ class ShardedDenoiser:
         self.text_tokens, self.image_tokens = text.shape[0], tokens - text.shape[0]
         self.mu = schedule.dynamic_mu(self.image_tokens) if mu is None else mu
         first, count = runner.rows
-        self.text_count = max(0, min(first + count, self.text_tokens) - first)
-        self.image_rows = (max(first, self.text_tokens) - self.text_tokens, count - self.text_count)
+        self.text_count, image_first, image_count = share_of_image(first, count, self.text_tokens)
+        self.image_rows = (image_first, image_count)
         self.text_local = text[first:first + self.text_count].contiguous()
         with torch.cuda.stream(runner.stream):
             runner.cos.copy_(cos.view(tokens, -1)[first:first + count], non_blocking=True)

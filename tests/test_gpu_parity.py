@@ -254,6 +254,7 @@ RANDOM_GEMMS = [
     (33, 16384, 16448, 256),
     (1043, 3072, 3072, 768),
     (515, 192, 256, 512),
+    (300, 256, 320, 32768),  # three 128-row halves: the launcher takes 128-row tiles here (3 rounds instead of 4)
 ]
 
 
@@ -307,6 +308,9 @@ FULL_SIZE = [
     ("down", 4608, 16384, 6144, "wide"),
     ("qkv_3072", 4608, 3072, 9216, "plain"),
     ("ragged", 4115, 6144, 6144, "resid"),
+    # row counts with an odd number of 128-row halves, where 128-row tiles save a round over the SMs
+    ("quarter_share_qkvg", 1152, 6144, 15360, "plain"),
+    ("bench_list_1043_gate_up", 1043, 6144, 32768, "swiglu"),
 ]
 
 

@@ -39,6 +39,25 @@ def test_shard_rows_gives_equal_shares_and_a_short_last_one():
         parallel.shard_rows(64, 0)
 
 
+def test_row_shares_cut_the_text_and_image_rows_without_gaps():
+    """The token-sharded loop: each rank's rows of [text; image] as text rows plus a range of image rows; over the
+    ranks the image ranges tile the image exactly, wherever the text/image boundary falls."""
+    from krea2_hrx_b200 import pipeline
+    for tokens, text_tokens, world in [(4608, 512, 8), (4608, 512, 4), (131, 70, 3), (300, 1, 4), (300, 299, 4), (16896, 512, 8)]:
+        next_image, text_seen = 0, 0
+        for first, count in parallel.shard_rows(tokens, world):
+            text_count, image_first, image_count = pipeline.share_of_image(first, count, text_tokens)
+            assert text_count + image_count == count and text_count >= 0 and image_count >= 0
+            if image_count:
+                assert image_first == next_image
+                next_image += image_count
+            text_seen += text_count
+        assert next_image == tokens - text_tokens and text_seen == text_tokens
+    assert pipeline.share_of_image(0, 44, 70) == (44, 0, 0)  # a rank of text rows only
+    assert pipeline.share_of_image(44, 44, 70) == (26, 0, 18)
+    assert pipeline.share_of_image(88, 43, 70) == (0, 18, 43)
+
+
 def _row_gather_worker(rank, world, port, failures):
     """The token-sharded chain's NCCL baseline on gloo: equal padded shares all-gathered into the rows of the
     full K tensor; rows past the sequence land beyond `tokens` and are never read."""
