@@ -133,7 +133,7 @@ def test_bad_arguments_are_refused():
     s.close()
 
 
-@pytest.mark.parametrize("world,text_tokens,image_tokens", [(2, 16, 120), (4, 40, 91), (3, 70, 61)])
+@pytest.mark.parametrize("world,text_tokens,image_tokens", [(2, 16, 120), (4, 40, 91), (3, 70, 61), (8, 50, 206)])
 def test_the_token_sharded_loop_equals_the_loop_on_one_device(world, text_tokens, image_tokens):
     """Every rank keeps to its rows of [text; image] through all steps (ranks emulated on this GPU, their launches
     interleaved stage by stage); the rows each rank owns must equal the single-device loop's, full block with
