@@ -1247,12 +1247,32 @@ extern "C" int krea2_attention_gqa_f16_rows(krea2_stream stream, size_t q_rows, 
     args.out_stride = static_cast<uint32_t>(out_stride);
     args.scale_log2 = scale * 1.4426950408889634f;
     args.out = static_cast<uint16_t *>(out);
-    // KREA2_ATTENTION_FORM=1 selects the one-tile-per-CTA form for A/B runs; the two-tile form is the default
-    // (measured at 4608 tokens: 0.477 ms against 0.518 ms per launch, 0.534 J against 0.581 J).
-    static const bool single_tile = [] {
+    // Two forms of the kernel give the same bits (same products, same softmax, same order).  With two query tiles
+    // per CTA a launch is shorter when the SMs are full for several rounds (measured at 4608 tokens: 0.477 ms
+    // against 0.518 ms, 0.534 J against 0.581 J); with one tile per CTA the CTAs are half as long, which wins when
+    // that saves rounds over the SMs -- few query rows, e.g. a device's share of a token-sharded sequence
+    // (1152 rows of 4608, 48 heads: 3 half-length rounds instead of 2 full ones, 0.135 ms against 0.163 ms).
+    // KREA2_ATTENTION_FORM=0 / 1 forces the two-tile / one-tile form.
+    static const int forced_form = [] {
         const char *v = getenv("KREA2_ATTENTION_FORM");
-        return v && v[0] == '1';
+        return v && (v[0] == '0' || v[0] == '1') ? v[0] - '0' : -1;
     }();
+    bool single_tile = forced_form == 1;
+    if (forced_form < 0) {
+        static int sm_counts[64] = {};  // per device, read once (benign race: every writer stores the same value)
+        int device = 0, sms = 0;
+        if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64) {
+            sms = sm_counts[device];
+            if (sms == 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess)
+                sm_counts[device] = sms;
+        }
+        if (sms > 0) {
+            const size_t heads = q_stride / 128;
+            const size_t pair_rounds = ((q_rows + 2 * kTile - 1) / (2 * kTile) * heads + sms - 1) / sms;
+            const size_t tile_rounds = ((q_rows + kTile - 1) / kTile * heads + sms - 1) / sms;
+            single_tile = tile_rounds * 543 < pair_rounds * 970;  // a one-tile CTA takes 0.543 of a two-tile CTA's time
+        }
+    }
     if (single_tile) {
         dim3 grid(static_cast<unsigned>((q_rows + kTile - 1) / kTile), static_cast<unsigned>(q_stride / 128), 1);
         attention_single_kernel<<<grid, kSingleThreads, kSingleSmemBytes, static_cast<cudaStream_t>(stream)>>>(

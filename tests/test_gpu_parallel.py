@@ -99,6 +99,31 @@ def test_attention_of_a_row_range_equals_those_rows_of_the_full_launch():
         assert torch.equal(part.view(torch.int16), full[first:first + count].view(torch.int16)), (first, count)
     with pytest.raises(k.InvalidArgument):
         ops.attention_gqa_rows(tokens + 1, tokens, kvh, q, kk, vt, full, qh * 128, kvh * 128, qh * 128, capacity, 0.0883883)
+
+
+def test_a_share_of_the_rows_through_the_one_tile_form_equals_the_two_tile_launch():
+    """The launcher takes one query tile per CTA when that saves rounds over the SMs and two otherwise; both forms
+    must give the same bits.  2000 tokens of 48 heads fill the SMs for three rounds of two-tile CTAs (the full
+    launch); a share of 1152 rows needs two such rounds or three half-length ones, so it goes through the other
+    form."""
+    from krea2_hrx_b200 import ops, shape
+    tokens, qh, kvh = 2000, 48, 12
+    capacity = shape.capacity(tokens)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    q = torch.randn((tokens, qh * 128), generator=gen, device="cuda").to(torch.float16)
+    kk = torch.randn((tokens, kvh * 128), generator=gen, device="cuda").to(torch.float16)
+    v = torch.randn((tokens, kvh * 128), generator=gen, device="cuda").to(torch.float16)
+    vt = torch.zeros((kvh * 128, capacity), dtype=torch.float16, device="cuda")
+    ops.v_transpose(v, vt, kvh * 128, capacity)
+    full = torch.zeros((tokens, qh * 128), dtype=torch.float16, device="cuda")
+    ops.attention_gqa(tokens, kvh, q, kk, vt, full, qh * 128, kvh * 128, qh * 128, capacity, 0.0883883)
+    for first, count in [(300, 1152), (0, 1043), (1700, 300)]:
+        part = torch.full((count, qh * 128), 9.0, dtype=torch.float16, device="cuda")
+        ops.attention_gqa_rows(count, tokens, kvh, q[first:first + count].contiguous(), kk, vt, part, qh * 128, kvh * 128,
+                               qh * 128, capacity, 0.0883883)
+        torch.cuda.synchronize()
+        assert torch.equal(part.view(torch.int16), full[first:first + count].view(torch.int16)), (first, count)
+    assert k.device_status() == 0
     assert k.device_status() == 0
 
 
