@@ -745,9 +745,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ---------------------------------------------------------------- attention, one query tile per CTA
-// The second form of the kernel, kept selectable (KREA2_ATTENTION_FORM=1) but not the default: it is correct
-// under the same tests and about 9 % slower than the two-tile form, because four softmax warps -- one per
-// scheduler -- cannot keep the exponential unit and the issue slots as busy as eight do.
+// The second form of the kernel: bit-identical to the two-tile form and, with the SMs full for several rounds,
+// about 9 % slower, because four softmax warps -- one per scheduler -- cannot keep the exponential unit and the
+// issue slots as busy as eight do.  Its CTAs are half as long, so the launcher takes it where that saves rounds
+// over the SMs (few query rows); KREA2_ATTENTION_FORM=0 / 1 forces a form.
 // A CTA owns ONE query tile of 128 rows and gives it everything the first form splits between two tiles.  Tensor memory (512 columns): S twice (2 x 128), O (128), P (64), Q (64).
 //  - Q sits in tensor memory (f16 pairs, the A-operand layout), so S = Q K^T reads only K from shared memory;
 //  - S is double-buffered and P has columns of its own, which breaks the chain S -> softmax -> P V -> next S of
