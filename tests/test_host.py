@@ -210,3 +210,22 @@ def test_the_reference_arm_prints_the_benchmark_line(tmp_path):
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in line["config"]
+
+
+def test_the_bench_reads_every_gemm_row_of_the_committed_dram_table():
+    """`roofline.traffic` and `kernels.*.dram_over_algorithmic` come from `profiles/gemm_i8_dram_bytes_m4608.md`;
+    a reworded table must not silently empty them.  The measured reads can never be below what a launch must read
+    at least once, nor absurdly above it."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    table, where = bench.profiled_dram_bytes()
+    assert where == os.path.join("profiles", "gemm_i8_dram_bytes_m4608.md")
+    assert set(table) == set(bench.GEMM_LABELS) and len(table) == 4
+    dims = dict(hidden=6144, kv_heads=12, head_dim=128, inter=16384)
+    for label, (m, n, k) in bench.gemm_shapes(dims, 4608).items():
+        read, written = table[label]
+        operands = m * k + n * k
+        assert 0.95 * operands <= read <= 3.0 * operands, (label, read, operands)
+        assert 0 < written <= bench.gemm_algorithmic_bytes(label, m, n, k), label
