@@ -515,7 +515,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const uint32_t s = j % kKvStages, phase = (j / kKvStages) & 1u;
                 const uint32_t next = (j + 1) % kKvStages, next_phase = ((j + 1) / kKvStages) & 1u;
                 const bool more = j + 1 < tiles;
-                // The operands of this round (V of tile j, K of tile j + 1) were requested long ago: they are
+                // The operands of this iteration (V of tile j, K of tile j + 1) were requested long ago: they are
                 // waited for first, so that nothing stands between a group's P arriving and its products.
                 alive = mbar_wait(v_full + s, phase, abort_flag) && (!more || mbar_wait(k_full + next, next_phase, abort_flag));
                 if (!alive) break;
