@@ -22,6 +22,11 @@ int fail(krea2_status status, const char *format, ...) {
 
 void clear_error() { g_last_error[0] = '\0'; }
 
+bool &dependent_launches() {
+    static thread_local bool flag = false;
+    return flag;
+}
+
 }  // namespace krea2
 
 using namespace krea2;

@@ -64,6 +64,7 @@ rope_qknorm_kernel(const uint16_t *__restrict__ qkv, const float *__restrict__ q
                    const float *__restrict__ sin_table, uint16_t *__restrict__ q_out, uint16_t *__restrict__ k_out,
                    uint16_t *__restrict__ v_out, uint32_t row_stride, uint32_t q_heads, uint32_t kv_heads,
                    uint32_t k_offset, float eps, const RowPush push) {
+    chain_wait();
     const size_t row = blockIdx.x;
     const size_t kv_row = S ? row + push.first_row : row;  // the row of the full-length K and V tensors
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = lane * 4;
@@ -157,6 +158,7 @@ __global__ void shard_signal_kernel(const RowPush push) {
 __global__ void __launch_bounds__(256)
 v_transpose_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ out, uint32_t rows, uint32_t width,
                    uint32_t capacity) {
+    chain_wait();
     __shared__ uint16_t tile[32][34];
     const uint32_t row0 = blockIdx.x * 32, col0 = blockIdx.y * 32;
     const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -459,6 +461,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;  // S (then P) of groups A and B at columns 0 and 128, their O at 256 and 384
+    chain_wait();  // everything above touched only this CTA's shared and tensor memory
 
     if (warp == kTmaWarpAttn) {
         if (lane == 0) {
@@ -827,6 +830,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    chain_wait();  // everything above touched only this CTA's shared and tensor memory
 
     if (warp == kSingleKWarp) {
         if (lane == 0) {
@@ -1077,8 +1081,8 @@ int make_f16_map(CUtensorMap *map, const void *base, size_t inner, size_t rows, 
     return KREA2_OK;
 }
 
-int launch_check(const char *what) {
-    cudaError_t status = cudaGetLastError();
+int launch_check(const char *what, cudaError_t launched = cudaSuccess) {
+    cudaError_t status = launched != cudaSuccess ? launched : cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "%s launch failed: %s", what, cudaGetErrorString(status));
     return KREA2_OK;
 }
@@ -1137,11 +1141,12 @@ extern "C" int krea2_rope_qknorm_f16(krea2_stream stream, size_t tokens, const v
     KREA2_REQUIRE(aligned16(qkv) && aligned16(q_scale) && aligned16(k_scale) && aligned16(cos_table) && aligned16(sin_table) &&
                       aligned16(q_out) && aligned16(k_out) && aligned16(v_out),
                   "rope_qknorm_f16: buffers must be 16-byte aligned");
-    rope_qknorm_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const cudaError_t launched = launch_chain_kernel(
+        rope_qknorm_kernel<false>, dim3(static_cast<unsigned>(tokens)), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const uint16_t *>(qkv), q_scale, k_scale, cos_table, sin_table, static_cast<uint16_t *>(q_out),
         static_cast<uint16_t *>(k_out), static_cast<uint16_t *>(v_out), static_cast<uint32_t>(row_stride),
         static_cast<uint32_t>(q_heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(k_offset), eps, RowPush{});
-    return launch_check("rope_qknorm_f16");
+    return launch_check("rope_qknorm_f16", launched);
 }
 
 namespace {
@@ -1212,10 +1217,11 @@ extern "C" int krea2_v_transpose(krea2_stream stream, size_t rows, const void *x
     KREA2_REQUIRE(rows >= 1 && rows <= row_capacity, "v_transpose: rows %zu outside 1..row_capacity", rows);
     KREA2_REQUIRE(x && out, "v_transpose: null buffer");
     dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>(width / 32), 1);
-    v_transpose_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t *>(x), static_cast<uint16_t *>(out), static_cast<uint32_t>(rows),
-        static_cast<uint32_t>(width), static_cast<uint32_t>(row_capacity));
-    return launch_check("v_transpose");
+    const cudaError_t launched = launch_chain_kernel(
+        v_transpose_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t *>(x),
+        static_cast<uint16_t *>(out), static_cast<uint32_t>(rows), static_cast<uint32_t>(width),
+        static_cast<uint32_t>(row_capacity));
+    return launch_check("v_transpose", launched);
 }
 
 extern "C" int krea2_attention_gqa_f16_rows(krea2_stream stream, size_t q_rows, size_t tokens, size_t kv_heads, const void *q,
@@ -1276,13 +1282,15 @@ extern "C" int krea2_attention_gqa_f16_rows(krea2_stream stream, size_t q_rows, 
     }
     if (single_tile) {
         dim3 grid(static_cast<unsigned>((q_rows + kTile - 1) / kTile), static_cast<unsigned>(q_stride / 128), 1);
-        attention_single_kernel<<<grid, kSingleThreads, kSingleSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-            map_k, map_v, static_cast<const uint16_t *>(q), static_cast<uint32_t>(q_stride), args);
-        return launch_check("attention");
+        const cudaError_t launched =
+            launch_chain_kernel(attention_single_kernel, grid, dim3(kSingleThreads), kSingleSmemBytes, static_cast<cudaStream_t>(stream),
+                                map_k, map_v, static_cast<const uint16_t *>(q), static_cast<uint32_t>(q_stride), args);
+        return launch_check("attention", launched);
     }
     dim3 grid(static_cast<unsigned>((q_rows + 2 * kTile - 1) / (2 * kTile)), static_cast<unsigned>(q_stride / 128), 1);
-    attention_kernel<<<grid, kAttnThreads, kAttnSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, args);
-    return launch_check("attention");
+    const cudaError_t launched = launch_chain_kernel(attention_kernel, grid, dim3(kAttnThreads), kAttnSmemBytes,
+                                                     static_cast<cudaStream_t>(stream), map_q, map_k, map_v, args);
+    return launch_check("attention", launched);
 }
 
 extern "C" int krea2_attention_gqa_lds_f16_wmma(krea2_stream stream, size_t tokens, size_t kv_heads, const void *q,

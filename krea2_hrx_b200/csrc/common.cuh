@@ -45,8 +45,41 @@ int prepare_gated_pitched(cudaStream_t stream, size_t tokens, const void *attn, 
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---------------------------------------------------------------- dependent launches
+// While a session queues the launches of a block chain it raises this thread-local flag: the chain's kernels are
+// then launched with programmatic stream serialization, so a kernel's blocks may start -- and run up to their
+// chain_wait() -- while the last blocks of the kernel before it are still running.  Every kernel of the chain
+// calls chain_wait() before its first access to global memory; without the launch attribute that call returns at
+// once, so the same kernels serve ordinary launches.
+bool &dependent_launches();
+
+template <typename... Params, typename... Args>
+cudaError_t launch_chain_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                                Args &&...args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute = {};
+    if (dependent_launches()) {
+        attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute.val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Args &&>(args)...);
+}
+
 // ---------------------------------------------------------------- device arithmetic
 #ifdef __CUDACC__
+
+// Waits until the kernels this launch depends on have completed and their writes are visible, then lets the next
+// launch of the chain start its blocks early in turn (they stop at their own chain_wait()).
+__device__ __forceinline__ void chain_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 // f32 -> bf16 -> f32, round to nearest even (the `fptrunc ... to bf16` + `extf` pairs of the
 // reference kernels; src/numerics.rs:18-26 states the rule).

@@ -701,6 +701,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    chain_wait();  // everything above touched only this CTA's shared and tensor memory
 
     if (warp == kProducerWarp) {
         if (lane == 0) {
@@ -888,6 +889,7 @@ gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     cluster_sync_all();  // barriers of both CTAs are initialised and the allocation is visible
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    chain_wait();  // everything above touched only the pair's shared and tensor memory
 
     if (warp == kProducerWarp) {
         if (lane == 0) {
@@ -1088,8 +1090,9 @@ int launch_instance(cudaStream_t stream, const CUtensorMap &map_a, const CUtenso
     if (int status = ensure_instance<E, BN, S>()) return status;
     const uint32_t tiles = ((args.m + kBlockM - 1) / kBlockM) * (args.n / BN);
     const unsigned grid = tiles < static_cast<uint32_t>(sm_count()) ? tiles : static_cast<unsigned>(sm_count());
-    gemm_i8_kernel<E, BN, S><<<grid, kGemmThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_w, args);
-    cudaError_t status = cudaGetLastError();
+    cudaError_t status = launch_chain_kernel(gemm_i8_kernel<E, BN, S>, dim3(grid), dim3(kGemmThreads), Tile<BN>::kSmemBytes, stream,
+                                             map_a, map_w, args);
+    if (status == cudaSuccess) status = cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 launch failed: %s", cudaGetErrorString(status));
     return KREA2_OK;
 }
@@ -1135,8 +1138,9 @@ int launch_pair(cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap
     if (int status = ensure_pair_instance<E, S>(&clusters)) return status;
     const uint32_t tiles = ((args.m + 2 * kBlockM - 1) / (2 * kBlockM)) * (args.n / PairTile::kBN);
     const unsigned pairs = tiles < static_cast<uint32_t>(clusters) ? tiles : static_cast<unsigned>(clusters);
-    gemm_i8_pair_kernel<E, S><<<2 * pairs, kGemmThreads, PairTile::kSmemBytes, stream>>>(map_a, map_w, args);
-    cudaError_t status = cudaGetLastError();
+    cudaError_t status = launch_chain_kernel(gemm_i8_pair_kernel<E, S>, dim3(2 * pairs), dim3(kGemmThreads), PairTile::kSmemBytes,
+                                             stream, map_a, map_w, args);
+    if (status == cudaSuccess) status = cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "gemm_i8 (two-CTA) launch failed: %s", cudaGetErrorString(status));
     return KREA2_OK;
 }

@@ -346,6 +346,7 @@ prepare_norm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ no
                     const float *__restrict__ mod_scale, const float *__restrict__ mod_shift,
                     int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride, float eps,
                     size_t tokens) {
+    chain_wait();
     using G = Geometry<CPL, kWideThreads>;
     using Plan = NormPlan<CPL>;
     constexpr int width = G::kWidth;
@@ -531,6 +532,7 @@ __global__ void __launch_bounds__(Geometry<CPL, kWideThreads>::kBlockThreads, 1)
 prepare_gated_kernel(const uint16_t *__restrict__ attn, const uint16_t *__restrict__ gate,
                      int8_t *__restrict__ q, float *__restrict__ q_scale, size_t out_stride,
                      size_t gate_stride, size_t attn_stride, size_t tokens) {
+    chain_wait();
     using G = Geometry<CPL, kWideThreads>;
     constexpr int kWarps = 2 * CPL;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -633,6 +635,7 @@ template <int CPL, bool kRotated>
 __global__ void __launch_bounds__(Geometry<CPL, kPlainThreads>::kBlockThreads, 1)
 prepare_plain_kernel(const uint16_t *__restrict__ h, int8_t *__restrict__ q, float *__restrict__ q_scale,
                      size_t out_stride, size_t tokens) {
+    chain_wait();
     using G = Geometry<CPL, kPlainThreads>;
     constexpr int width = G::kWidth;
     constexpr int kWarps = 2 * CPL;
@@ -754,8 +757,8 @@ int dispatch_width(size_t width, Args... args) {
     return fail(KREA2_INTERNAL, "no prologue instance for width %zu", width);
 }
 
-int finish_launch(const char *what) {
-    cudaError_t status = cudaGetLastError();
+int finish_launch(const char *what, cudaError_t launched = cudaSuccess) {
+    cudaError_t status = launched != cudaSuccess ? launched : cudaGetLastError();
     if (status != cudaSuccess) return fail(KREA2_RUNTIME, "%s launch failed: %s", what, cudaGetErrorString(status));
     return KREA2_OK;
 }
@@ -802,10 +805,11 @@ struct LaunchNorm {
         int device = 0;
         if (int s = current_device(&device)) return s;
         if (int s = allow_shared(prepare_norm_kernel<CPL>, NormPlan<CPL>::kBytes, done, device)) return s;
-        prepare_norm_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
-                                   NormPlan<CPL>::kBytes, stream>>>(
-            static_cast<const uint16_t *>(h), ns, ms, sh, static_cast<int8_t *>(q), q_scale, out_stride, eps, tokens);
-        return finish_launch("prepare_norm_i8");
+        const cudaError_t launched = launch_chain_kernel(
+            prepare_norm_kernel<CPL>, dim3(persistent_grid(device, tokens, G::kWorkers)), dim3(G::kBlockThreads),
+            NormPlan<CPL>::kBytes, stream, static_cast<const uint16_t *>(h), ns, ms, sh, static_cast<int8_t *>(q), q_scale,
+            out_stride, eps, tokens);
+        return finish_launch("prepare_norm_i8", launched);
     }
 };
 
@@ -833,11 +837,11 @@ struct LaunchGated {
         if (int s = current_device(&device)) return s;
         if (int s = allow_shared(prepare_gated_kernel<CPL>, GatedPlan<CPL>::kBytes, done, device)) return s;
         if (int s = ensure_sigmoid_table(stream, device)) return s;
-        prepare_gated_kernel<CPL><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
-                                    GatedPlan<CPL>::kBytes, stream>>>(
-            static_cast<const uint16_t *>(attn), static_cast<const uint16_t *>(gate), static_cast<int8_t *>(q),
-            q_scale, out_stride, gate_stride, attn_stride, tokens);
-        return finish_launch("prepare_gated_i8");
+        const cudaError_t launched = launch_chain_kernel(
+            prepare_gated_kernel<CPL>, dim3(persistent_grid(device, tokens, G::kWorkers)), dim3(G::kBlockThreads),
+            GatedPlan<CPL>::kBytes, stream, static_cast<const uint16_t *>(attn), static_cast<const uint16_t *>(gate),
+            static_cast<int8_t *>(q), q_scale, out_stride, gate_stride, attn_stride, tokens);
+        return finish_launch("prepare_gated_i8", launched);
     }
 };
 
@@ -850,10 +854,11 @@ struct LaunchPlainAs {
         int device = 0;
         if (int s = current_device(&device)) return s;
         if (int s = allow_shared(prepare_plain_kernel<CPL, kRotated>, PlainPlan<CPL>::kBytes, done, device)) return s;
-        prepare_plain_kernel<CPL, kRotated><<<persistent_grid(device, tokens, G::kWorkers), G::kBlockThreads,
-                                              PlainPlan<CPL>::kBytes, stream>>>(
-            static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride, tokens);
-        return finish_launch(kRotated ? "prepare_rotated_i8" : "prepare_plain_i8");
+        const cudaError_t launched = launch_chain_kernel(
+            prepare_plain_kernel<CPL, kRotated>, dim3(persistent_grid(device, tokens, G::kWorkers)), dim3(G::kBlockThreads),
+            PlainPlan<CPL>::kBytes, stream, static_cast<const uint16_t *>(h), static_cast<int8_t *>(q), q_scale, out_stride,
+            tokens);
+        return finish_launch(kRotated ? "prepare_rotated_i8" : "prepare_plain_i8", launched);
     }
 };
 template <int CPL>

@@ -155,6 +155,7 @@ struct krea2_session {
     bool attention = true;  // false: the W8A8 chain alone, the query columns in the attention output's place
     bool fused_rotation = false;  // the gate|up epilogue starts the down projection's rotation (same bits either way)
     bool fused_rope = false;      // the q|k|v|gate epilogue does the QK-norm + RoPE launch's work (same bits either way)
+    bool dependent_launch = false;  // the chain's launches let the next kernel's blocks start under the last blocks of this one
     bool rope_valid = false;
     uint64_t rope_print[2] = {0, 0};
     std::vector<Stage> stages;
@@ -222,6 +223,11 @@ constexpr bool kFusedRotationDefault = false;
 // The same for the q|k|v|gate GEMM doing the QK-norm + RoPE launch's work (krea2_gemm_i8_rope_256);
 // KREA2_FUSED_ROPE=0/1 overrides it.
 constexpr bool kFusedRopeDefault = false;
+// Whether the launches of a forward carry the programmatic-stream-serialization attribute (every launch but the
+// first, and none in a profiled forward, whose events sit between the kernels); KREA2_DEPENDENT_LAUNCH=0/1
+// overrides it.  The kernels wait for their predecessor before their first global access, so the results do
+// not change.
+constexpr bool kDependentLaunchDefault = false;
 
 // One block's launches in the reference's order.  `events`, when given, receives one event before
 // every stage and one after the last; `labels`, when given, the stage labels in launch order.
@@ -243,9 +249,14 @@ int run_block(krea2_session *s, cudaStream_t stream, size_t index, cudaEvent_t *
         return KREA2_OK;
     };
     int status = KREA2_OK;
-#define KREA2_STEP(label, call)                  \
-    if ((status = mark(label))) return status;   \
-    if ((status = (call))) return status;
+    // The very first launch of a forward follows copies, not a kernel: it is an ordinary launch.
+    const bool chain = s->dependent_launch && events == nullptr;
+#define KREA2_STEP(label, call)                                 \
+    if ((status = mark(label))) return status;                  \
+    dependent_launches() = chain && !(index == 0 && stage == 1); \
+    status = (call);                                            \
+    dependent_launches() = false;                               \
+    if (status) return status;
     KREA2_STEP("prepare", krea2_prepare_norm_i8(stream, t, s->x, w.prenorm, mods, mods + hidden, s->a_q, s->a_s, hidden, ph,
                                                 1e-5f))
     const bool rope_in_gemm = s->attention && s->fused_rope;
@@ -569,6 +580,8 @@ extern "C" int krea2_session_create(krea2_stream stream, krea2_weights *weights,
     p->fused_rotation = fused ? std::string(fused) == "1" : kFusedRotationDefault;
     const char *rope = getenv("KREA2_FUSED_ROPE");
     p->fused_rope = (rope ? std::string(rope) == "1" : kFusedRopeDefault) && p->qkvg % 256 == 0;
+    const char *dependent = getenv("KREA2_DEPENDENT_LAUNCH");
+    p->dependent_launch = dependent ? std::string(dependent) == "1" : kDependentLaunchDefault;
     *out = guard.release();
     return KREA2_OK;
 }

@@ -165,6 +165,41 @@ def test_run_device_refuses_tensors_of_the_wrong_kind(small):
     s.close()
 
 
+@pytest.mark.parametrize("tokens", [97, 700])
+def test_dependent_launches_change_no_bit(small, tokens, monkeypatch):
+    """With KREA2_DEPENDENT_LAUNCH=1 a session's launches carry the programmatic-stream-serialization attribute: a
+    kernel's blocks start under the last blocks of the kernel before it and wait for it before their first global
+    access.  Same kernels, same order: the full block (attention on) must give the same bytes, eagerly, replayed from
+    the graph and in a profiled forward (which falls back to ordinary launches)."""
+    from krea2_hrx_b200 import session
+    dims, weights, host = small
+    stream = torch.cuda.current_stream()
+    layers = 3
+    x, mods, cos, sin = so.make_inputs(dims, tokens, layers, seed=33)
+    args = (torch.from_numpy(mods), torch.from_numpy(cos), torch.from_numpy(sin))
+    monkeypatch.delenv("KREA2_DEPENDENT_LAUNCH", raising=False)
+    plain = session.Session(stream, weights, tokens, layers)
+    want = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    plain.run(stream, want, *args)
+    monkeypatch.setenv("KREA2_DEPENDENT_LAUNCH", "1")
+    chained = session.Session(stream, weights, tokens, layers)
+    for _ in range(3):  # the first call records the graph, the others replay it
+        got = torch.from_numpy(x.copy()).view(torch.bfloat16)
+        chained.run(stream, got, *args)
+        np.testing.assert_array_equal(bits(got), bits(want))
+    x_dev = torch.from_numpy(x.copy()).view(torch.bfloat16).cuda()
+    chained.run_device(stream, x_dev, args[0].cuda(), args[1], args[2])
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(bits(x_dev.cpu()), bits(want))
+    chained.set_profile(True)
+    got = torch.from_numpy(x.copy()).view(torch.bfloat16)
+    chained.run(stream, got, *args)
+    np.testing.assert_array_equal(bits(got), bits(want))
+    assert k.device_status() == 0
+    plain.close()
+    chained.close()
+
+
 def test_profiled_forward_reports_the_reference_stage_labels(small):
     """src/session/mod.rs:461-494, 627-647."""
     from krea2_hrx_b200 import session
