@@ -21,6 +21,11 @@ HIDDEN, KV_HEADS, HEAD_DIM, INTER = 6144, 12, 128, 16384  # src/session/mod.rs:3
 SEED, LAYERS = 20240611, 2
 TEXT_TOKENS, GRID_H, GRID_W = 16, 4, 8
 TOKENS = TEXT_TOKENS + GRID_H * GRID_W  # 48
+# A second case over the same weights whose sequence spans several 128-key tiles of the attention kernel, the
+# last one ragged: one block, and the fixture keeps a sample of the output rows.
+LONG_GRID_H, LONG_GRID_W = 12, 16
+LONG_TOKENS = TEXT_TOKENS + LONG_GRID_H * LONG_GRID_W  # 208
+LONG_ROWS = sorted(set(range(0, LONG_TOKENS, 4)) | set(range(LONG_TOKENS - 8, LONG_TOKENS)) | {1, 15, 16, 17, 127, 129})
 
 
 def block_tensors(layers: int = LAYERS, seed: int = SEED) -> "OrderedDict[str, np.ndarray]":
@@ -60,11 +65,11 @@ def bf16_round(values: np.ndarray) -> np.ndarray:
     return rounded.astype(np.uint32).view(np.float32)
 
 
-def block_inputs(layers: int = LAYERS, seed: int = SEED):
-    """x (f32 holding bf16 values, [TOKENS][HIDDEN]) and the per-block modulation (f32 holding bf16
+def block_inputs(layers: int = LAYERS, seed: int = SEED, tokens: int = TOKENS, stream: int = 1000):
+    """x (f32 holding bf16 values, [tokens][HIDDEN]) and the per-block modulation (f32 holding bf16
     values, [layers][6][HIDDEN]: prescale, preshift, pregate, postscale, postshift, postgate)."""
-    rng = np.random.Generator(np.random.PCG64([seed, 1000]))
-    x = bf16_round(rng.standard_normal((TOKENS, HIDDEN)).astype(np.float32))
+    rng = np.random.Generator(np.random.PCG64([seed, stream]))
+    x = bf16_round(rng.standard_normal((tokens, HIDDEN)).astype(np.float32))
     mods = (rng.standard_normal((layers, 6, HIDDEN)) * 0.3).astype(np.float32)
     return x, bf16_round(mods)
 
@@ -85,3 +90,8 @@ def oracle_blocks(tensors, layers: int = LAYERS):
             entry[name] = spans[f"{p}{name}"]["image"].view(np.float32)
         out.append(entry)
     return out
+
+
+def long_inputs():
+    """The inputs of the several-tile case: 208 tokens, one block."""
+    return block_inputs(layers=1, tokens=LONG_TOKENS, stream=1001)

@@ -1,4 +1,4 @@
-"""Generates tests/golden/block_w8a8.npz from the reference's own torch transformer block.
+"""Generates tests/golden/block_w8a8.npz and block_w8a8_long.npz from the reference's own torch transformer block.
 
 Run once in a checkout that has the krea2-hrx sources beside it:
     python tests/golden/make_block_golden.py /path/to/krea2-hrx
@@ -8,7 +8,8 @@ unmodified, builds the seeded synthetic weights of tests/block_case.py under the
 names, and runs `Krea2Ref.block` (:262-268: RMSNorm + adaLN, q|k|v|gate, QK-norm, RoPE, attention,
 sigmoid gate, wo, residual, RMSNorm + adaLN, SwiGLU, down, residual) with `quant="w8a8"` on the CPU
 in bf16 for one and for two blocks.  The fixture records the inputs (x, modulation, cos, sin) and
-the residual stream after each block.
+the residual stream after each block.  A second fixture holds one block over 208 tokens (two key tiles
+of the attention kernel, the second ragged): the rope tables and a sample of the output rows.
 
 The scheme rotates with a dense normalised Hadamard matrix in f32, quantises with a division,
 multiplies in f32 and has bf16 rounding only where torch's bf16 tensors impose it, so it is a
@@ -60,6 +61,17 @@ def main():
             out[f"after_block_{i}"] = bits(x[0])
     np.savez_compressed(os.path.join(HERE, "block_w8a8.npz"), **out)
     print({name: value.shape for name, value in out.items()})
+    # The several-tile case: 208 tokens through block 0; x and the modulation are regenerated from the seed by
+    # the tests, the fixture keeps the rope tables and a sample of the output rows.
+    x32, mods32 = block_case.long_inputs()
+    cos, sin = ref.rope_tables(ref.position_ids(block_case.TEXT_TOKENS, block_case.LONG_GRID_H, block_case.LONG_GRID_W, "cpu"))
+    x = torch.from_numpy(x32).to(torch.bfloat16)[None]
+    with torch.no_grad():
+        x = model.block(0, x, torch.from_numpy(mods32).to(torch.bfloat16)[0], cos, sin)
+    rows = np.asarray(block_case.LONG_ROWS, dtype=np.int64)
+    long_out = {"cos": cos.numpy(), "sin": sin.numpy(), "rows": rows, "after_block_0_rows": bits(x[0])[rows]}
+    np.savez_compressed(os.path.join(HERE, "block_w8a8_long.npz"), **long_out)
+    print({name: value.shape for name, value in long_out.items()})
 
 
 if __name__ == "__main__":

@@ -52,3 +52,22 @@ def test_the_oracle_chain_with_float64_attention_tracks_the_reference_block(case
     delta_got = oracle.bf16_bits_to_f32(got).astype(np.float64) - x0
     delta_want = oracle.bf16_bits_to_f32(want).astype(np.float64) - x0
     assert np.linalg.norm(delta_got - delta_want) / np.linalg.norm(delta_want) < 0.04
+
+
+def test_the_oracle_chain_tracks_the_reference_block_over_several_key_tiles(case):
+    """208 tokens: the attention spans two 128-key tiles, the second ragged.  tests/golden/block_w8a8_long.npz holds
+    the reference block's output rows `rows`; x and the modulation are regenerated from the seed."""
+    from krea2_hrx_b200 import session
+    _, blocks = case
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "block_w8a8_long.npz"))
+    x, mods = block_case.long_inputs()
+    assert list(golden["rows"]) == block_case.LONG_ROWS and golden["cos"].shape == (block_case.LONG_TOKENS, block_case.HEAD_DIM)
+    got, _ = session_oracle.oracle_forward(session.ModelDims(), blocks, oracle.f32_to_bf16_bits(x), mods, count=1,
+                                           attention=True, cos=golden["cos"], sin=golden["sin"])
+    rel = session_oracle.relative_l2(got[golden["rows"]], golden["after_block_0_rows"])
+    print(f"oracle chain vs Krea2Ref, 208 tokens, 1 block: relative RMS {rel:.5f}")
+    assert rel < BOUNDS[1]
+    x0 = x[golden["rows"]].astype(np.float64)
+    delta_got = oracle.bf16_bits_to_f32(got[golden["rows"]]).astype(np.float64) - x0
+    delta_want = oracle.bf16_bits_to_f32(golden["after_block_0_rows"]).astype(np.float64) - x0
+    assert np.linalg.norm(delta_got - delta_want) / np.linalg.norm(delta_want) < 0.04

@@ -53,3 +53,23 @@ def test_the_session_with_attention_tracks_the_reference_block(loaded, count):
     assert rel < BOUNDS[count]
     assert k.device_status() == 0
     s.close()
+
+
+def test_the_session_tracks_the_reference_block_over_several_key_tiles(loaded):
+    """208 tokens, one block: the attention kernel walks two key tiles, the second ragged, against the reference
+    block's own softmax (tests/golden/block_w8a8_long.npz: the rope tables and a sample of the output rows)."""
+    import oracle
+    weights, _ = loaded
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "block_w8a8_long.npz"))
+    x32, mods = block_case.long_inputs()
+    stream = torch.cuda.current_stream()
+    s = session.Session(stream, weights, block_case.LONG_TOKENS, 1)
+    s.set_attention(True)
+    x = torch.from_numpy(oracle.f32_to_bf16_bits(x32).view(np.int16).copy()).view(torch.bfloat16)
+    s.run(stream, x, torch.from_numpy(mods.copy()), torch.from_numpy(golden["cos"]), torch.from_numpy(golden["sin"]))
+    got = x.view(torch.int16).numpy().view(np.uint16)[golden["rows"]]
+    rel = session_oracle.relative_l2(got, golden["after_block_0_rows"])
+    print(f"CUDA session vs Krea2Ref, 208 tokens, 1 block: relative RMS {rel:.5f}")
+    assert rel < BOUNDS[1]
+    assert k.device_status() == 0
+    s.close()
