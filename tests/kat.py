@@ -235,3 +235,37 @@ def convrot_expected(weights, scales, x_bf16) -> np.ndarray:
         base = (dot.astype(np.float32) * scales) * scale
         out[t] = bf16_bits_from_f32(base.astype(np.float32))
     return out
+
+
+def swiglu_golden_accumulators(path):
+    """tests/golden/swiglu_bf16.npz as the accumulators of a one-row gate|up GEMM: (acc [1][n], channel scales [n],
+    expected f32 values [n/2], valid outputs).  Gate and up columns interleave in sixteens as the kernel expects."""
+    g = np.load(path)
+    gate, up = g["gate_acc"].reshape(-1), g["up_acc"].reshape(-1)
+    outputs = gate.size
+    padded = -(-outputs // 128) * 128
+    gate = np.concatenate([gate, np.zeros(padded - outputs, np.int32)])
+    up = np.concatenate([up, np.zeros(padded - outputs, np.int32)])
+    acc = np.stack([gate.reshape(-1, 16), up.reshape(-1, 16)], axis=1).reshape(1, -1).astype(np.int32)
+    want = (g["product"].reshape(-1).astype(np.uint32) << 16).view(np.float32)
+    scale = np.tile(np.concatenate([np.full(16, 2.0 ** -15), np.full(16, 2.0 ** -8)]), acc.shape[1] // 32).astype(np.float32)
+    return acc, scale, want, outputs
+
+
+def weights_for_accumulators(acc_row, k=512):
+    """int8 A [1][k] and W [n][k] whose product is `acc_row`: A is 127 over the first k-128 positions and 1 over the
+    last 128, so W's first part carries round(acc / 127) spread over entries of at most 127 and its last part the
+    remainder."""
+    n = acc_row.size
+    a = np.concatenate([np.full(k - 128, 127, np.int8), np.ones(128, np.int8)])[None, :]
+    coarse = np.rint(acc_row / 127.0).astype(np.int64)
+    rest = acc_row.astype(np.int64) - 127 * coarse
+    assert np.all(np.abs(rest) <= 64) and np.all(np.abs(coarse) <= 127 * (k - 128))
+    w = np.zeros((n, k), np.int64)
+    slots = k - 128
+    base, extra = np.divmod(np.abs(coarse), slots)
+    w[:, :slots] = (base[:, None] + (np.arange(slots)[None, :] < extra[:, None])) * np.sign(coarse)[:, None]
+    w[:, slots] = rest  # one position of weight 1 holds the remainder
+    assert np.all(np.abs(w) <= 127)
+    assert np.array_equal((a.astype(np.int64) @ w.T)[0], acc_row.astype(np.int64))
+    return a, w.astype(np.int8)

@@ -222,3 +222,16 @@ def test_attention_repeated_dispatch_is_deterministic(ops):
             kat.close(kat.f16_from_bits(got[rows]).astype(np.float64), want, 2e-2, 2e-2)
         else:
             np.testing.assert_array_equal(got, first)
+
+
+def test_qk_norm_and_rope_equal_the_reference_torch_code_bit_for_bit(ops):
+    """The CUDA kernel against tests/golden/rope_qknorm.npz (the reference's own `rms_norm` + `apply_rope` on its own
+    rope tables, made by tests/golden/make_rope_golden.py): q and k are the reference's bf16 values exactly."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "rope_qknorm.npz"))
+    fused = oracle.bf16_bits_to_f32(g["fused"])
+    inp = fused.astype(np.float16).view(np.uint16)
+    q, kk, v = run_rope(ops, inp, g["q_scale"], g["k_scale"], g["cos"], g["sin"], 1536, 8, 2)
+    np.testing.assert_array_equal(q.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["q"]))
+    np.testing.assert_array_equal(kk.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["k"]))
+    np.testing.assert_array_equal(v.view(np.float16).astype(np.float32), fused[:, 10 * 128:])

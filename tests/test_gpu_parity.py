@@ -471,3 +471,25 @@ def test_fused_convrot_call_equals_the_launch_sequence(ops, inputs):
     small = torch.empty(16, dtype=torch.uint8, device="cuda")
     with pytest.raises(k.InvalidArgument, match="workspace"):
         layer.forward_fused(stream, x, small)
+
+
+def test_the_swiglu_kernel_equals_torchs_silu_product_bit_for_bit(ops):
+    """The CUDA gate|up GEMM against tests/golden/swiglu_bf16.npz (`F.silu(g) * u` on bf16 tensors, the statement of
+    `Krea2Ref.swiglu`, scripts/quantized_reference.py:222-225): int8 operands are built whose exact products are the
+    fixture's accumulators, so the epilogue sees every bf16 gate value with an exponent from -8 to 6."""
+    import os
+    acc, scale, want, outputs = kat.swiglu_golden_accumulators(os.path.join(os.path.dirname(__file__), "golden", "swiglu_bf16.npz"))
+    k_size, got = 512, []
+    cut = acc.shape[1] // 512 * 256  # two launches of whole 256-column tiles, each within the 32768-column limit
+    for part in (slice(0, cut), slice(cut, acc.shape[1])):
+        columns = part.stop - part.start
+        assert columns % 256 == 0 and columns <= 32768
+        a, w = kat.weights_for_accumulators(acc[0, part], k_size)
+        c = torch.zeros((1, columns // 2), dtype=torch.float16, device="cuda")
+        ops.gemm_i8_swiglu_256(1, dev(a), dev(w), dev(scale[part]), dev(np.ones(1, np.float32)), c, k_size, k_size, columns)
+        torch.cuda.synchronize()
+        got.append(c.cpu().numpy().astype(np.float32)[0])
+    got = np.concatenate(got)[:outputs]
+    normal = np.abs(want) >= 2.0 ** -14
+    np.testing.assert_array_equal(got[normal], want[normal])
+    assert np.abs(got - want)[~normal].max() <= 2.0 ** -25

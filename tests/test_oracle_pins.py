@@ -1,4 +1,6 @@
 """Pins the CPU oracle to the reference's own known-answer tests (restated in kat.py)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -123,3 +125,32 @@ def test_oracle_tracks_the_reference_torch_scheme(name):
     ref = kat.f16_from_bits(g["out"]).astype(np.float64)
     rel_l2 = np.linalg.norm(out - ref) / np.linalg.norm(ref)
     assert rel_l2 < 1e-2, rel_l2
+
+
+def test_qk_norm_and_rope_equal_the_reference_torch_code_bit_for_bit():
+    """tests/golden/rope_qknorm.npz: `rms_norm` and `apply_rope` of scripts/quantized_reference.py (:71-73, :158-162),
+    imported unmodified by tests/golden/make_rope_golden.py and applied as `Krea2Ref.attention` applies them (:211-214),
+    with the reference's own rope tables.  Both sides round to bf16 after the norm and after the rotation, so the
+    oracle's q and k must be the reference's bf16 values exactly (an f16 holds them); V is copied through."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "rope_qknorm.npz"))
+    fused = oracle.bf16_bits_to_f32(g["fused"])
+    as_f16 = fused.astype(np.float16)
+    assert np.array_equal(as_f16.astype(np.float32), fused), "the inputs are exact in f16"
+    q, k, v = oracle.rope_qknorm_f16(as_f16.view(np.uint16), g["q_scale"], g["k_scale"], g["cos"], g["sin"], 1536, 8, 2, 8 * 128)
+    np.testing.assert_array_equal(q.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["q"]))
+    np.testing.assert_array_equal(k.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["k"]))
+    np.testing.assert_array_equal(v.view(np.float16).astype(np.float32), fused[:, 10 * 128:])
+
+
+def test_the_swiglu_epilogue_equals_torchs_silu_product_bit_for_bit():
+    """tests/golden/swiglu_bf16.npz: `F.silu(g) * u` on bf16 tensors, the statement of `Krea2Ref.swiglu`
+    (scripts/quantized_reference.py:222-225), made by tests/golden/make_swiglu_golden.py: every bf16 gate value with an
+    exponent from -8 to 6 against eight up values.  Both sides round the SiLU and the product to bf16; the kernel's f16
+    output holds every such value of normal f16 magnitude exactly, smaller ones to an f16 subnormal step."""
+    acc, scale, want, outputs = kat.swiglu_golden_accumulators(os.path.join(os.path.dirname(__file__), "golden", "swiglu_bf16.npz"))
+    c = oracle.epilogue_swiglu(acc, scale, np.ones(1, np.float32))
+    got = c.view(np.float16).astype(np.float32)[0][:outputs]
+    normal = np.abs(want) >= 2.0 ** -14
+    assert normal.sum() > 27000
+    np.testing.assert_array_equal(got[normal], want[normal])
+    assert np.abs(got - want)[~normal].max() <= 2.0 ** -25
