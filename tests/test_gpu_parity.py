@@ -493,3 +493,23 @@ def test_the_swiglu_kernel_equals_torchs_silu_product_bit_for_bit(ops):
     normal = np.abs(want) >= 2.0 ** -14
     np.testing.assert_array_equal(got[normal], want[normal])
     assert np.abs(got - want)[~normal].max() <= 2.0 ** -25
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_the_residual_kernels_equal_torchs_gated_update_bit_for_bit(ops, wide):
+    """Both residual exports against tests/golden/resid_bf16.npz (`x + gate * a` on bf16 tensors, the residual update
+    of `Krea2Ref.block`, scripts/quantized_reference.py:262-268), through int8 operands whose exact products are the
+    fixture's accumulators."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "resid_bf16.npz"))
+    n, k_size = g["acc"].size, 1024
+    a, w = kat.weights_for_accumulators(g["acc"], k_size)
+    c = dev(g["x"][None, :].view(np.int16), torch.bfloat16)
+    gate = dev(oracle.bf16_bits_to_f32(g["gate"]))
+    scale, ones = dev(np.full(n, 2.0 ** -12, np.float32)), dev(np.ones(1, np.float32))
+    if wide:
+        ops.gemm_i8_resid_256x256(1, dev(a), dev(w), scale, ones, c, gate, k_size, k_size, n, schedule_rows=0)
+    else:
+        ops.gemm_i8_resid_256(1, dev(a), dev(w), scale, ones, c, gate, k_size, k_size, n)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(c.view(torch.int16).cpu().numpy().view(np.uint16)[0], g["out"])

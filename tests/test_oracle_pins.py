@@ -154,3 +154,14 @@ def test_the_swiglu_epilogue_equals_torchs_silu_product_bit_for_bit():
     assert normal.sum() > 27000
     np.testing.assert_array_equal(got[normal], want[normal])
     assert np.abs(got - want)[~normal].max() <= 2.0 ** -25
+
+
+def test_the_residual_epilogue_equals_torchs_gated_update_bit_for_bit():
+    """tests/golden/resid_bf16.npz: `x + gate * a` on bf16 tensors, the residual update of `Krea2Ref.block`
+    (scripts/quantized_reference.py:262-268), made by tests/golden/make_resid_golden.py: the product and the sum each
+    round to bf16, cancellation and absorption included."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "resid_bf16.npz"))
+    acc = g["acc"][None, :]
+    out = oracle.epilogue_resid(acc, np.full(acc.shape[1], 2.0 ** -12, np.float32), np.ones(1, np.float32), g["x"][None, :],
+                                oracle.bf16_bits_to_f32(g["gate"]))
+    np.testing.assert_array_equal(out[0], g["out"])
