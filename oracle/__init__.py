@@ -113,6 +113,26 @@ def prepare_norm_i8(h, norm_scale, mod_scale, mod_shift, width, out_stride, eps=
     return q, s
 
 
+def norm_modulate(h, norm_scale, mod_scale, mod_shift, width, eps=1e-5):
+    """The front half of prepare_norm_i8 -- RMSNorm with `1 + norm_scale`, then adaLN -- as bf16 bits [tokens][width]:
+    what the Hadamard rotation receives."""
+    h = np.ascontiguousarray(h, dtype=np.uint16).reshape(-1, width)
+    ns, ms, sh = (np.ascontiguousarray(v, dtype=np.float32) for v in (norm_scale, mod_scale, mod_shift))
+    out = np.zeros_like(h)
+    lib().oracle_norm_modulate(_sz(h.shape[0]), _p(h), _p(ns), _p(ms), _p(sh), _p(out), _sz(width), ctypes.c_float(eps))
+    return out
+
+
+def gate_attention(attn, gate, width, gate_stride):
+    """The front half of prepare_gated_i8 -- attention output times bf16(sigmoid(gate)), rounded to bf16 -- as bf16
+    bits [tokens][width]; attn and gate are f16 bits."""
+    attn = np.ascontiguousarray(attn, dtype=np.uint16).reshape(-1, width)
+    gate = np.ascontiguousarray(gate, dtype=np.uint16).reshape(-1, gate_stride)
+    out = np.zeros_like(attn)
+    lib().oracle_gate_attention(_sz(attn.shape[0]), _p(attn), _p(gate), _p(out), _sz(width), _sz(gate_stride))
+    return out
+
+
 def prepare_gated_i8(attn, gate, width, out_stride, gate_stride, fill=0):
     """attn: f16 bits [tokens][width]; gate: f16 bits [tokens][gate_stride]."""
     attn = np.ascontiguousarray(attn, dtype=np.uint16).reshape(-1, width)

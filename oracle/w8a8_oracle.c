@@ -191,49 +191,67 @@ static void quantise_row(const float *x, size_t width, float rotation, int8_t *q
  * ((a0+a1)+(a2+a3))+((a4+a5)+(a6+a7)); the 32 lanes of a wave fold by the xor
  * butterfly 16, 8, 4, 2, 1.  The eight wave sums combine as the reference writes:
  * ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)).  rsqrt is 1/sqrt, both correctly rounded. */
+/* The front half of prepare_norm_i8 for one row: RMSNorm with `1 + norm_scale`, then adaLN, every product and the
+ * sum rounded to bf16 (kernels/prepare_norm_i8.loom:120-172); x receives the bf16 values as f32. */
+static void norm_modulate_row(const uint16_t *row, const float *norm_scale, const float *mod_scale,
+                              const float *mod_shift, float *x, size_t width, float eps) {
+    size_t chunks_per_lane = width / 2048;
+    float lane_sum[256];
+    for (size_t l = 0; l < 256; l++) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (size_t j = 0; j < chunks_per_lane; j++) {
+            const uint16_t *c = row + (j * 256 + l) * 8;
+            for (int e = 0; e < 8; e++) {
+                float v = bf16_to_f32(c[e]);
+                float sq = v * v;
+                acc[e] = acc[e] + sq;
+            }
+        }
+        lane_sum[l] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+    }
+    float p[8];
+    for (size_t w = 0; w < 8; w++) {
+        float v[32], n[32];
+        memcpy(v, lane_sum + w * 32, sizeof v);
+        for (int off = 16; off >= 1; off >>= 1) {
+            for (int i = 0; i < 32; i++) n[i] = v[i] + v[i ^ off];
+            memcpy(v, n, sizeof v);
+        }
+        p[w] = v[0];
+    }
+    float total = ((p[0] + p[4]) + (p[2] + p[6])) + ((p[1] + p[5]) + (p[3] + p[7]));
+    float mean = total / (float)(int32_t)width;
+    float mean_eps = mean + eps;
+    float rinv = 1.0f / sqrtf(mean_eps);
+    for (size_t i = 0; i < width; i++) {
+        float v = bf16_to_f32(row[i]);
+        float n = v * rinv;
+        float ns1 = norm_scale[i] + 1.0f;
+        float normed = bf(n * ns1);
+        float ms1 = bf(mod_scale[i] + 1.0f);
+        float scaled = bf(normed * ms1);
+        x[i] = bf(scaled + mod_shift[i]);
+    }
+}
+
+/* The same for `tokens` rows, as bf16 bits: what the Hadamard rotation of prepare_norm_i8 receives.  Test
+ * infrastructure for holding that stage to the reference's torch statement of it. */
+void oracle_norm_modulate(size_t tokens, const uint16_t *h, const float *norm_scale, const float *mod_scale,
+                          const float *mod_shift, uint16_t *out, size_t width, float eps) {
+    float *x = (float *)malloc(width * sizeof(float));
+    for (size_t t = 0; t < tokens; t++) {
+        norm_modulate_row(h + t * width, norm_scale, mod_scale, mod_shift, x, width, eps);
+        for (size_t i = 0; i < width; i++) out[t * width + i] = f32_to_bf16(x[i]);
+    }
+    free(x);
+}
+
 void oracle_prepare_norm_i8(size_t tokens, const uint16_t *h, const float *norm_scale,
                             const float *mod_scale, const float *mod_shift, int8_t *q,
                             float *q_scale, size_t width, size_t out_stride, float eps) {
-    size_t chunks_per_lane = width / 2048;
     float *x = (float *)malloc(width * sizeof(float));
     for (size_t t = 0; t < tokens; t++) {
-        const uint16_t *row = h + t * width;
-        float lane_sum[256];
-        for (size_t l = 0; l < 256; l++) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (size_t j = 0; j < chunks_per_lane; j++) {
-                const uint16_t *c = row + (j * 256 + l) * 8;
-                for (int e = 0; e < 8; e++) {
-                    float v = bf16_to_f32(c[e]);
-                    float sq = v * v;
-                    acc[e] = acc[e] + sq;
-                }
-            }
-            lane_sum[l] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
-        }
-        float p[8];
-        for (size_t w = 0; w < 8; w++) {
-            float v[32], n[32];
-            memcpy(v, lane_sum + w * 32, sizeof v);
-            for (int off = 16; off >= 1; off >>= 1) {
-                for (int i = 0; i < 32; i++) n[i] = v[i] + v[i ^ off];
-                memcpy(v, n, sizeof v);
-            }
-            p[w] = v[0];
-        }
-        float total = ((p[0] + p[4]) + (p[2] + p[6])) + ((p[1] + p[5]) + (p[3] + p[7]));
-        float mean = total / (float)(int32_t)width;
-        float mean_eps = mean + eps;
-        float rinv = 1.0f / sqrtf(mean_eps);
-        for (size_t i = 0; i < width; i++) {
-            float v = bf16_to_f32(row[i]);
-            float n = v * rinv;
-            float ns1 = norm_scale[i] + 1.0f;
-            float normed = bf(n * ns1);
-            float ms1 = bf(mod_scale[i] + 1.0f);
-            float scaled = bf(normed * ms1);
-            x[i] = bf(scaled + mod_shift[i]);
-        }
+        norm_modulate_row(h + t * width, norm_scale, mod_scale, mod_shift, x, width, eps);
         hadamard256_f32(x, width);
         quantise_row(x, width, 0.0625f, q + t * out_stride, q_scale + t);
     }
@@ -242,16 +260,34 @@ void oracle_prepare_norm_i8(size_t tokens, const uint16_t *h, const float *norm_
 
 /* kernels/prepare_gated_i8.loom:18-313: a = bf16(attn), sigma = bf16(1/(1+exp(-g))),
  * o = bf16(a*sigma) (:86-108), then the f32 rotation and quantisation of the norm kernel. */
+/* The front half of prepare_gated_i8 for one row: the attention output times the sigmoid of the gate, the
+ * sigmoid and the product rounded to bf16 (kernels/prepare_gated_i8.loom:86-108). */
+static void gate_row(const uint16_t *attn, const uint16_t *gate, float *x, size_t width) {
+    for (size_t i = 0; i < width; i++) {
+        float a = bf(f16_to_f32(attn[i]));
+        float g = f16_to_f32(gate[i]);
+        float sig = bf(sigmoid_f32(g));
+        x[i] = bf(a * sig);
+    }
+}
+
+/* The same for `tokens` rows, as bf16 bits: what the Hadamard rotation of prepare_gated_i8 receives.  Test
+ * infrastructure for holding that stage to the reference's torch statement of it. */
+void oracle_gate_attention(size_t tokens, const uint16_t *attn, const uint16_t *gate, uint16_t *out, size_t width,
+                           size_t gate_stride) {
+    float *x = (float *)malloc(width * sizeof(float));
+    for (size_t t = 0; t < tokens; t++) {
+        gate_row(attn + t * width, gate + t * gate_stride, x, width);
+        for (size_t i = 0; i < width; i++) out[t * width + i] = f32_to_bf16(x[i]);
+    }
+    free(x);
+}
+
 void oracle_prepare_gated_i8(size_t tokens, const uint16_t *attn, const uint16_t *gate, int8_t *q,
                              float *q_scale, size_t width, size_t out_stride, size_t gate_stride) {
     float *x = (float *)malloc(width * sizeof(float));
     for (size_t t = 0; t < tokens; t++) {
-        for (size_t i = 0; i < width; i++) {
-            float a = bf(f16_to_f32(attn[t * width + i]));
-            float g = f16_to_f32(gate[t * gate_stride + i]);
-            float sig = bf(sigmoid_f32(g));
-            x[i] = bf(a * sig);
-        }
+        gate_row(attn + t * width, gate + t * gate_stride, x, width);
         hadamard256_f32(x, width);
         quantise_row(x, width, 0.0625f, q + t * out_stride, q_scale + t);
     }

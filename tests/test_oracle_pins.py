@@ -165,3 +165,25 @@ def test_the_residual_epilogue_equals_torchs_gated_update_bit_for_bit():
     out = oracle.epilogue_resid(acc, np.full(acc.shape[1], 2.0 ** -12, np.float32), np.ones(1, np.float32), g["x"][None, :],
                                 oracle.bf16_bits_to_f32(g["gate"]))
     np.testing.assert_array_equal(out[0], g["out"])
+
+
+def test_rmsnorm_and_adaln_equal_the_reference_torch_expression_bit_for_bit():
+    """tests/golden/norm_modulate.npz: `(1.0 + prescale) * rms_norm(x, scale) + preshift` on bf16 tensors, the argument
+    `Krea2Ref.block` hands to its attention and MLP (scripts/quantized_reference.py:265, :267; `rms_norm` imported
+    unmodified by tests/golden/make_norm_golden.py).  The front half of prepare_norm_i8 -- the sum of squares in the
+    kernel's order, 1/sqrt, and four bf16 roundings -- must give the same bf16 values on all 73,728 of them."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "norm_modulate.npz"))
+    got = oracle.norm_modulate(g["x"], g["scale"], oracle.bf16_bits_to_f32(g["prescale"]), oracle.bf16_bits_to_f32(g["preshift"]),
+                               g["x"].shape[1])
+    np.testing.assert_array_equal(got, g["out"])
+
+
+def test_the_attention_gate_equals_torchs_sigmoid_product_bit_for_bit():
+    """tests/golden/gate_attention.npz: `o * torch.sigmoid(gate)` on bf16 tensors (`Krea2Ref.attention`,
+    scripts/quantized_reference.py:219), every bf16 gate value with an exponent from -8 to 6.  The front half of
+    prepare_gated_i8 -- the canonical exp, the reciprocal and two bf16 roundings -- must give the same bf16 values."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "gate_attention.npz"))
+    as_f16 = lambda b: oracle.bf16_bits_to_f32(b).astype(np.float16).view(np.uint16)
+    n = g["gate"].size
+    got = oracle.gate_attention(as_f16(g["attn"]).reshape(1, n), as_f16(g["gate"]).reshape(1, n), n, n)
+    np.testing.assert_array_equal(got.reshape(-1), g["out"].reshape(-1))
