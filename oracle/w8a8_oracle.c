@@ -10,7 +10,11 @@
  * compiler (the 8-wide and 32-lane sum reductions, the approximate exp, rsqrt) this
  * file fixes ONE order, documented at the function, and the CUDA kernels are held
  * to that order bit for bit.  Those spots are "parity unpinned" against the
- * reference at the ulp level; the reference's own tests tolerate +-1 code there.
+ * reference's kernels at the ulp level; the reference's own tests tolerate +-1 code
+ * there.  Each of them feeds a bf16 rounding, and against the reference's torch code
+ * (scripts/quantized_reference.py, imported by the scripts under tests/golden/) the
+ * bf16 results are equal on every fixture value: RMSNorm + adaLN, the attention gate,
+ * QK-norm + RoPE, the SwiGLU product, the residual update.
  * Everything else (the Hadamard butterflies, bf16/f16 rounding points, quantisation,
  * the i32 dot, the three epilogues) is pinned by the reference's tests, restated in
  * tests/test_oracle_pins.py.
