@@ -235,3 +235,33 @@ def test_qk_norm_and_rope_equal_the_reference_torch_code_bit_for_bit(ops):
     np.testing.assert_array_equal(q.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["q"]))
     np.testing.assert_array_equal(kk.view(np.float16).astype(np.float32), oracle.bf16_bits_to_f32(g["k"]))
     np.testing.assert_array_equal(v.view(np.float16).astype(np.float32), fused[:, 10 * 128:])
+
+
+def test_attention_tracks_torchs_scaled_dot_product_attention(ops):
+    """The CUDA kernel against tests/golden/attention_sdpa.npz (`F.scaled_dot_product_attention` on bf16 tensors with
+    repeated key/value heads, `Krea2Ref.attention`, scripts/quantized_reference.py:215-218): 208 tokens, two key tiles
+    with the second ragged, eight query heads over two key/value heads.  The tolerance is the reference attention
+    test's (tests/quantized.rs:309-383); torch's own bf16 output rounding is most of the difference."""
+    import importlib.util
+    import os
+    from krea2_hrx_b200 import shape
+    golden = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("make_attention_golden", os.path.join(golden, "make_attention_golden.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    q, k, v = module.inputs()
+    want = oracle.bf16_bits_to_f32(np.load(os.path.join(golden, "attention_sdpa.npz"))["out"])
+    tokens, qh, kvh = module.TOKENS, module.Q_HEADS, module.KV_HEADS
+    capacity = shape.capacity(tokens)
+    q_d, k_d, v_d = (torch.from_numpy(a.astype(np.float16)).cuda() for a in (q, k, v))
+    vt = torch.zeros((kvh * 128, capacity), dtype=torch.float16, device="cuda")
+    ops.v_transpose(v_d, vt, kvh * 128, capacity)
+    out = torch.zeros((tokens, qh * 128), dtype=torch.float16, device="cuda")
+    ops.attention_gqa(tokens, kvh, q_d, k_d, vt, out, qh * 128, kvh * 128, qh * 128, capacity, float(1.0 / np.sqrt(128.0)))
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().astype(np.float32)
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-2 + 2e-2 * np.abs(want))
+    rel = float(np.sqrt((err ** 2).sum() / (want ** 2).sum()))
+    print(f"CUDA attention vs torch SDPA (bf16), 208 tokens: relative RMS {rel:.5f}")
+    assert rel < 0.004

@@ -187,3 +187,27 @@ def test_the_attention_gate_equals_torchs_sigmoid_product_bit_for_bit():
     n = g["gate"].size
     got = oracle.gate_attention(as_f16(g["attn"]).reshape(1, n), as_f16(g["gate"]).reshape(1, n), n, n)
     np.testing.assert_array_equal(got.reshape(-1), g["out"].reshape(-1))
+
+
+def _sdpa_case():
+    import importlib.util
+    golden = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("make_attention_golden", os.path.join(golden, "make_attention_golden.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)  # only its seeded `inputs()` is used; torch is imported but not called
+    q, k, v = module.inputs()
+    want = oracle.bf16_bits_to_f32(np.load(os.path.join(golden, "attention_sdpa.npz"))["out"])
+    return q, k, v, want
+
+
+def test_float64_attention_tracks_torchs_scaled_dot_product_attention():
+    """tests/golden/attention_sdpa.npz: `F.scaled_dot_product_attention` on bf16 tensors with the key/value heads
+    repeated over their query groups (`Krea2Ref.attention`, scripts/quantized_reference.py:215-218); 208 tokens, eight
+    query heads over two key/value heads.  torch's output is bf16, so the float64 oracle is held to the tolerance of the
+    reference's attention test (tests/quantized.rs:309-383) and to a relative RMS of half a bf16 step."""
+    q, k, v, want = _sdpa_case()
+    as_f16 = lambda a: a.astype(np.float16).view(np.uint16)
+    got = oracle.attention_gqa(as_f16(q), as_f16(k), as_f16(v), 8, 2, 1.0 / np.sqrt(128.0))
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-2 + 2e-2 * np.abs(want))
+    assert np.sqrt((err ** 2).sum() / (want ** 2).sum()) < 0.003
