@@ -95,3 +95,12 @@ def oracle_blocks(tensors, layers: int = LAYERS):
 def long_inputs():
     """The inputs of the several-tile case: 208 tokens, one block."""
     return block_inputs(layers=1, tokens=LONG_TOKENS, stream=1001)
+
+
+def modulation_inputs(layers: int = LAYERS, seed: int = SEED):
+    """The time model's modulation vector (f32 holding bf16 values, [6 * HIDDEN]) and the blocks' tables
+    `blocks.N.mod.lin` ([layers][6 * HIDDEN]) that `Krea2Ref.block_modulation` adds to it."""
+    rng = np.random.Generator(np.random.PCG64([seed, 1002]))
+    vector = bf16_round((rng.standard_normal(6 * HIDDEN) * 0.2).astype(np.float32))
+    tables = bf16_round((rng.standard_normal((layers, 6 * HIDDEN)) * 0.2).astype(np.float32))
+    return vector, tables

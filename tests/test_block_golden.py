@@ -71,3 +71,19 @@ def test_the_oracle_chain_tracks_the_reference_block_over_several_key_tiles(case
     delta_got = oracle.bf16_bits_to_f32(got[golden["rows"]]).astype(np.float64) - x0
     delta_want = oracle.bf16_bits_to_f32(golden["after_block_0_rows"]).astype(np.float64) - x0
     assert np.linalg.norm(delta_got - delta_want) / np.linalg.norm(delta_want) < 0.04
+
+
+def test_modulation_and_two_blocks_track_the_reference_blocks_forward(case):
+    """tests/golden/blocks_forward_w8a8.npz: `Krea2Ref.blocks_forward` (scripts/quantized_reference.py:270-273) -- per
+    block `block_modulation` (the shared vector plus the block's `mod.lin` table, :257-259) and `block` -- over the
+    48-token inputs.  Here: the oracle's modulation kernel feeds the oracle chain."""
+    from krea2_hrx_b200 import session
+    golden, blocks = case
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "blocks_forward_w8a8.npz"))["out"]
+    vector, tables = block_case.modulation_inputs()
+    mods = oracle.modulation(oracle.f32_to_bf16_bits(vector), oracle.f32_to_bf16_bits(tables)).reshape(block_case.LAYERS, 6, -1)
+    got, _ = session_oracle.oracle_forward(session.ModelDims(), blocks, golden["x"], mods, count=block_case.LAYERS,
+                                           attention=True, cos=golden["cos"], sin=golden["sin"])
+    rel = session_oracle.relative_l2(got, want)
+    print(f"oracle modulation + chain vs Krea2Ref.blocks_forward, 2 blocks: relative RMS {rel:.5f}")
+    assert rel < BOUNDS[2]

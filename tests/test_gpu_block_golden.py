@@ -73,3 +73,28 @@ def test_the_session_tracks_the_reference_block_over_several_key_tiles(loaded):
     assert rel < BOUNDS[1]
     assert k.device_status() == 0
     s.close()
+
+
+def test_modulation_and_the_session_track_the_reference_blocks_forward(loaded):
+    """`krea2_modulation` (the shared vector plus each block's table) feeding a two-block session, against
+    `Krea2Ref.blocks_forward` (scripts/quantized_reference.py:257-259, 270-273; tests/golden/blocks_forward_w8a8.npz)."""
+    import oracle
+    from krea2_hrx_b200 import ops
+    weights, golden = loaded
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "blocks_forward_w8a8.npz"))["out"]
+    vector, tables = block_case.modulation_inputs()
+    as_bf16 = lambda a: torch.from_numpy(oracle.f32_to_bf16_bits(a).view(np.int16).copy()).view(torch.bfloat16).cuda()
+    stream = torch.cuda.current_stream()
+    mods = torch.empty((block_case.LAYERS, 6, block_case.HIDDEN), dtype=torch.float32, device="cuda")
+    ops.modulation(as_bf16(vector), as_bf16(tables), mods, stream)
+    s = session.Session(stream, weights, block_case.TOKENS, block_case.LAYERS)
+    s.set_attention(True)
+    x = torch.from_numpy(golden["x"].copy()).view(torch.bfloat16).cuda()
+    s.run_device(stream, x, mods, torch.from_numpy(golden["cos"]), torch.from_numpy(golden["sin"]))
+    torch.cuda.synchronize()
+    got = x.cpu().view(torch.int16).numpy().view(np.uint16)
+    rel = session_oracle.relative_l2(got, want)
+    print(f"CUDA modulation + session vs Krea2Ref.blocks_forward, 2 blocks: relative RMS {rel:.5f}")
+    assert rel < BOUNDS[2]
+    assert k.device_status() == 0
+    s.close()
